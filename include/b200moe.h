@@ -1,0 +1,143 @@
+/*
+ * b200moe.h -- C ABI of the B200 (sm_100a) FP8 block-scale MoE layer.
+ *
+ * One handle = one rank's share of an MoE layer of a fixed shape.  All data pointers are
+ * DEVICE pointers unless stated otherwise; inputs are borrowed and never modified; every
+ * launch is enqueued on the caller's stream and no entry point synchronises the host unless
+ * its comment says so.  Every function returns 0 on success, a negative B200MOE_E_* code for
+ * an argument/setup error, or a positive cudaError_t value.
+ *
+ * The reference interfaces each entry point replaces are cited as path:line inside the
+ * reference corpus (OpenBMB/JustGoal), with
+ *   <def>  = moe_fp8_block_scale_ds_routing_topk8_ng8_kg4_e32_h7168_i2048
+ *   KF94/  = kda05_reproduction_full_shape/fable-5.1/moe_fp8_fwd/<def>/fable51_moe_v94/
+ *   GF/    = goal_full_shape/fable-5.1/moe_fp8_fwd/<def>/
+ *   SF1/   = goal_single_shape/fable-5.1/moe_fp8_fwd/t1/
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_ROUTING_DEEPSEEK 0      /* sigmoid + bias, group-limited top-k            */
+#define B200MOE_ROUTING_RENORM_NAIVE 1  /* softmax -> top-k -> renormalise (no groups)     */
+
+#define B200MOE_E_BADARG   (-1)   /* null pointer, negative size, unsupported shape        */
+#define B200MOE_E_WORKSPACE (-2)  /* workspace too small or misaligned                     */
+#define B200MOE_E_DRIVER   (-3)   /* cuTensorMapEncodeTiled unavailable / failed           */
+#define B200MOE_E_DEVICE   (-4)   /* not an sm_100 device                                  */
+#define B200MOE_E_KERNEL   (-5)   /* a kernel recorded a device-side error (see status)    */
+
+typedef struct b200moe_config {
+    int hidden;              /* H, multiple of 128                                         */
+    int intermediate;        /* I, multiple of 128                                         */
+    int num_experts;         /* E global, multiple of 32, <= 512                           */
+    int num_local_experts;   /* experts owned by this rank, <= 256                         */
+    int top_k;               /* <= 8                                                       */
+    int n_group;             /* DeepSeek routing: number of expert groups (else 1)         */
+    int topk_group;          /* DeepSeek routing: groups kept per token (else 1)           */
+    int routing_mode;        /* B200MOE_ROUTING_*                                          */
+} b200moe_config;
+
+typedef struct b200moe_ctx* b200moe_handle;
+
+/* Offsets (bytes from the workspace base) of the intermediates one forward leaves behind;
+ * for tests and debugging only. */
+typedef struct b200moe_ws_layout {
+    size_t status;        /* int32[8]: [0] device error word, [1] pairs P, [2] padded rows,
+                             [3] token tiles, [4] active experts                           */
+    size_t counts;        /* int32[E_local] tokens per local expert                        */
+    size_t expert_row0;   /* int32[E_local+1] first (padded) row of each expert            */
+    size_t tile_prefix;   /* int32[E_local+1] exclusive prefix of token tiles              */
+    size_t topk_idx;      /* int32[T, top_k] global expert ids                             */
+    size_t topk_w;        /* float[T, top_k]                                               */
+    size_t pair_row;      /* int32[T, top_k] row of a local pair (undefined if not local)  */
+    size_t row_token;     /* int32[rows_cap] token of a row, -1 for padding                */
+    size_t row_w;         /* float[rows_cap] routing weight of a row                       */
+    size_t a_perm;        /* uint8[rows_cap, H] expert-sorted fp8 activations              */
+    size_t a_scale_perm;  /* float[H/128, rows_cap]                                        */
+    size_t act_hi;        /* uint8[rows_cap, I] e4m3 of SwiGLU output / scale              */
+    size_t act_lo;        /* uint8[rows_cap, I] e4m3 of the rounding residual              */
+    size_t act_scale;     /* float[I/128, rows_cap]                                        */
+    size_t y;             /* float[rows_cap, H] weighted expert outputs per row            */
+    size_t rows_cap;      /* number of rows the row-indexed buffers hold                   */
+    size_t token_tile;    /* tokens per GEMM tile chosen for this T                        */
+    size_t total_bytes;
+} b200moe_ws_layout;
+
+/* Create / destroy a layer handle on the CURRENT device.  Does one-time kernel attribute
+ * setup.  Replaces the one-time setup block of the reference launcher
+ * (KF94/kernel.cu:5355-5402) and `moe_init` (SF1/kernel.py:40-44). */
+int b200moe_create(const b200moe_config* cfg, b200moe_handle* out);
+int b200moe_destroy(b200moe_handle h);
+
+/* Workspace the caller must provide for a forward over T tokens (256-byte aligned).
+ * Replaces `moe_ws_bytes` (SF1/kernel.py:40-44) and the Python-side `_workspace`
+ * allocation (KF94/main.py:147-193, GF/main.py:68-94). */
+int b200moe_workspace_bytes(b200moe_handle h, int num_tokens, size_t* bytes);
+int b200moe_workspace_layout(b200moe_handle h, int num_tokens, b200moe_ws_layout* layout);
+
+/* The operator: routing -> permute -> GEMM1+SwiGLU -> GEMM2 -> weighted combine.
+ *   routing_logits      float  [T, E]
+ *   routing_bias        bf16   [E] or NULL (= zeros)
+ *   hidden_states       e4m3   [T, H]
+ *   hidden_states_scale float  [H/128, T]
+ *   gemm1_weights       e4m3   [E_local, 2I, H]    gemm1_weights_scale float [E_local, 2I/128, H/128]
+ *   gemm2_weights       e4m3   [E_local, H, I]     gemm2_weights_scale float [E_local, H/128, I/128]
+ *   output              bf16   [T, H]  (every row is written; rows without a local expert = 0)
+ * Same argument order and meaning as the reference's C entry point
+ * `extern "C" int moe_run(...)` (KF94/kernel.cu:5336-5348) and its Python operator
+ * signature `run(...)` (GF/main.py:102-117, KF94/main.py:196-209). */
+int b200moe_forward(b200moe_handle h,
+                    const void* routing_logits, const void* routing_bias,
+                    const void* hidden_states, const void* hidden_states_scale,
+                    const void* gemm1_weights, const void* gemm1_weights_scale,
+                    const void* gemm2_weights, const void* gemm2_weights_scale,
+                    int num_tokens, int local_expert_offset, float routed_scaling_factor,
+                    void* output, void* workspace, size_t workspace_bytes, void* cuda_stream);
+
+/* Routing alone: writes int32 topk_idx[T, top_k] (global expert ids) and float
+ * topk_w[T, top_k].  Replaces the reference's exported `moe_routing`
+ * (goal_full_shape/opus-5/moe_fp8_fwd/<def>/moe_kernel.cu:1098-1101) and its
+ * `route_topk_kernel` launch (KF94/kernel.cu:5426-5431). */
+int b200moe_route(b200moe_handle h, const void* routing_logits, const void* routing_bias,
+                  int num_tokens, float routed_scaling_factor,
+                  int32_t* topk_idx, float* topk_w, void* cuda_stream);
+
+/* The expert part alone, for tokens that were routed elsewhere (expert-parallel receive
+ * side): like b200moe_forward but takes topk_idx/topk_w instead of logits, and writes the
+ * fp32 sum over the LOCAL experts to output_f32 [T, H] (no bf16 rounding, so partial sums
+ * of several ranks can be added before the single final rounding).  The reference has no
+ * expert-parallel code; this corresponds to the launcher's stages after routing
+ * (KF94/kernel.cu:5436-5586). */
+int b200moe_forward_routed(b200moe_handle h,
+                           const int32_t* topk_idx, const float* topk_w,
+                           const void* hidden_states, const void* hidden_states_scale,
+                           const void* gemm1_weights, const void* gemm1_weights_scale,
+                           const void* gemm2_weights, const void* gemm2_weights_scale,
+                           int num_tokens, int local_expert_offset,
+                           float* output_f32, void* workspace, size_t workspace_bytes,
+                           void* cuda_stream);
+
+/* Synchronises the stream, reads the device error word of the last forward on this
+ * workspace into *word (0 = no error) and returns B200MOE_E_KERNEL if it is non-zero.
+ * The reference returns cudaGetLastError() only (KF94/kernel.cu:5681); its device waits
+ * are unbounded, ours give up after a time limit and report here. */
+int b200moe_status(b200moe_handle h, const void* workspace, void* cuda_stream, int* word);
+
+/* Number of this library's kernels one forward over T tokens launches (a count of
+ * launches, not of kernels that do useful work). */
+int b200moe_launches_per_forward(b200moe_handle h, int num_tokens, int* launches);
+
+const char* b200moe_strerror(int code);
+int b200moe_num_sms(void);            /* cf. `moe_num_sms`, SF1/kernel.py:40-44 */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

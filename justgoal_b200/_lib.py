@@ -1,0 +1,61 @@
+"""ctypes binding of libb200moe.so (the C ABI in include/b200moe.h).
+
+There is no fallback: if the shared library is missing or does not load, importing this
+module raises.  Build it with `python -m justgoal_b200.build`.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200moe.so")
+
+
+class Config(C.Structure):
+    _fields_ = [("hidden", C.c_int), ("intermediate", C.c_int), ("num_experts", C.c_int),
+                ("num_local_experts", C.c_int), ("top_k", C.c_int), ("n_group", C.c_int),
+                ("topk_group", C.c_int), ("routing_mode", C.c_int)]
+
+
+class WsLayout(C.Structure):
+    _fields_ = [(n, C.c_size_t) for n in (
+        "status", "counts", "expert_row0", "tile_prefix", "topk_idx", "topk_w", "pair_row", "row_token",
+        "row_w", "a_perm", "a_scale_perm", "act_hi", "act_lo", "act_scale", "y", "rows_cap", "token_tile",
+        "total_bytes")]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} not found: build it with `python -m justgoal_b200.build` "
+                          "(there is no CPU or PyTorch fallback for this operator)")
+    lib = C.CDLL(LIB_PATH)
+    vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+    lib.b200moe_create.argtypes = [C.POINTER(Config), C.POINTER(vp)]
+    lib.b200moe_destroy.argtypes = [vp]
+    lib.b200moe_workspace_bytes.argtypes = [vp, i, C.POINTER(sz)]
+    lib.b200moe_workspace_layout.argtypes = [vp, i, C.POINTER(WsLayout)]
+    lib.b200moe_forward.argtypes = [vp] + [vp] * 8 + [i, i, f, vp, vp, sz, vp]
+    lib.b200moe_route.argtypes = [vp, vp, vp, i, f, vp, vp, vp]
+    lib.b200moe_forward_routed.argtypes = [vp, vp, vp] + [vp] * 6 + [i, i, vp, vp, sz, vp]
+    lib.b200moe_status.argtypes = [vp, vp, vp, C.POINTER(i)]
+    lib.b200moe_launches_per_forward.argtypes = [vp, i, C.POINTER(i)]
+    lib.b200moe_strerror.argtypes = [i]
+    lib.b200moe_strerror.restype = C.c_char_p
+    lib.b200moe_num_sms.argtypes = []
+    for name in ("create", "destroy", "workspace_bytes", "workspace_layout", "forward", "route",
+                 "forward_routed", "status", "launches_per_forward", "num_sms"):
+        getattr(lib, "b200moe_" + name).restype = i
+    return lib
+
+
+lib = _load()
+
+
+class B200MoEError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str = "b200moe"):
+    if rc != 0:
+        raise B200MoEError(f"{what} failed with code {rc}: {lib.b200moe_strerror(rc).decode()}")

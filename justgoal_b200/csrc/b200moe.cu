@@ -1,0 +1,393 @@
+// Host side of libb200moe: the C ABI declared in include/b200moe.h.
+//
+// Mirrors the job of the reference's host launcher (shape checks, tensor-map encoding, kernel
+// family choice by token count, launches on the caller's stream, integer return codes:
+// kda05_reproduction_full_shape/fable-5.1/moe_fp8_fwd/<def>/fable51_moe_v94/kernel.cu:5336-5682,
+// goal_full_shape/fable-5.1/moe_fp8_fwd/<def>/moe_host.cu:88-183) for kernels written from
+// scratch for sm_100a.  No torch types, no allocation inside forward, no host synchronisation
+// except in b200moe_status.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "../../include/b200moe.h"
+#include "common.cuh"
+#include "gemm.cuh"
+#include "permute.cuh"
+#include "routing.cuh"
+
+using namespace b200moe;
+
+struct b200moe_ctx {
+    b200moe_config cfg;
+    int device;
+    int num_sms;
+};
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// 2-D byte tensor [rows][cols] (cols contiguous), box [box_rows][128 bytes], 128-byte swizzle.
+int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return B200MOE_E_DRIVER;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : B200MOE_E_DRIVER;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Tokens per GEMM tile, from shapes only (never from data): the expected number of rows per
+// expert under uniform routing.
+int pick_token_tile(const b200moe_config& c, int T) {
+    const double avg = (double)T * c.top_k / c.num_experts;
+    if (avg <= 10.0) return 16;
+    if (avg <= 24.0) return 32;
+    if (avg <= 56.0) return 64;
+    return 128;
+}
+
+int rows_capacity(const b200moe_config& c, int T) {
+    const long long per_tok = c.top_k < c.num_local_experts ? c.top_k : c.num_local_experts;
+    long long rows = (long long)T * per_tok + (long long)ROW_ALIGN * c.num_local_experts;
+    rows = (rows + 127) / 128 * 128 + 128;
+    return (int)rows;
+}
+
+void layout(const b200moe_config& c, int T, b200moe_ws_layout* L) {
+    const size_t A = 256;
+    const int El = c.num_local_experts, K = c.top_k;
+    const size_t rows = (size_t)rows_capacity(c, T);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, A); return o; };
+    L->status = take(8 * 4);
+    L->counts = take((size_t)El * 4);
+    L->expert_row0 = take((size_t)(El + 1) * 4);
+    L->tile_prefix = take((size_t)(El + 1) * 4);
+    L->topk_idx = take((size_t)T * K * 4);
+    L->topk_w = take((size_t)T * K * 4);
+    L->pair_row = take((size_t)T * K * 4);
+    L->row_token = take(rows * 4);
+    L->row_w = take(rows * 4);
+    L->a_perm = take(rows * c.hidden);
+    L->a_scale_perm = take((size_t)(c.hidden / 128) * rows * 4);
+    L->act_hi = take(rows * c.intermediate);
+    L->act_lo = take(rows * c.intermediate);
+    L->act_scale = take((size_t)(c.intermediate / 128) * rows * 4);
+    L->y = take(rows * c.hidden * 4);
+    L->rows_cap = rows;
+    L->token_tile = (size_t)pick_token_tile(c, T);
+    L->total_bytes = off;
+}
+
+template <int NTOK, bool G1>
+cudaError_t set_attr() {
+    return cudaFuncSetAttribute(gemm_kernel<NTOK, G1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                GemmCfg<NTOK, G1>::SMEM_BYTES);
+}
+
+template <int NTOK, bool G1>
+cudaError_t launch_gemm(int grid, cudaStream_t st, const CUtensorMap& w, const CUtensorMap& b0, const CUtensorMap& b1,
+                        const GemmParams& p) {
+    gemm_kernel<NTOK, G1><<<grid, GemmCfg<NTOK, G1>::NTHREADS, GemmCfg<NTOK, G1>::SMEM_BYTES, st>>>(w, b0, b1, p);
+    return cudaGetLastError();
+}
+
+template <bool G1>
+cudaError_t launch_gemm_ntok(int ntok, int grid, cudaStream_t st, const CUtensorMap& w, const CUtensorMap& b0,
+                             const CUtensorMap& b1, const GemmParams& p) {
+    switch (ntok) {
+        case 16: return launch_gemm<16, G1>(grid, st, w, b0, b1, p);
+        case 32: return launch_gemm<32, G1>(grid, st, w, b0, b1, p);
+        case 64: return launch_gemm<64, G1>(grid, st, w, b0, b1, p);
+        default: return launch_gemm<128, G1>(grid, st, w, b0, b1, p);
+    }
+}
+
+bool cfg_ok(const b200moe_config& c) {
+    if (c.hidden <= 0 || c.hidden % 128 || c.intermediate <= 0 || c.intermediate % 128) return false;
+    if (c.num_experts <= 0 || c.num_experts % 32 || c.num_experts > 512) return false;
+    const int vpt = c.num_experts / 32;
+    if (vpt != 1 && vpt != 2 && vpt != 4 && vpt != 8 && vpt != 16) return false;
+    if (c.num_local_experts <= 0 || c.num_local_experts > MAX_LOCAL || c.num_local_experts > c.num_experts) return false;
+    if (c.top_k <= 0 || c.top_k > 8 || c.top_k > c.num_experts) return false;
+    if (c.routing_mode == B200MOE_ROUTING_DEEPSEEK) {
+        if (c.n_group <= 0 || c.num_experts % c.n_group) return false;
+        const int gs = c.num_experts / c.n_group;
+        if (gs % vpt) return false;                       // a group is a whole number of lanes
+        const int lpg = gs / vpt;
+        if (lpg & (lpg - 1)) return false;                // ... and a power of two of them
+        if (gs < 2) return false;                         // group score needs two experts
+        if (c.topk_group <= 0 || c.topk_group > c.n_group) return false;
+        if (c.topk_group * gs < c.top_k) return false;    // enough candidates for top_k
+    } else if (c.routing_mode != B200MOE_ROUTING_RENORM_NAIVE) {
+        return false;
+    }
+    return true;
+}
+
+template <int MODE>
+cudaError_t launch_route(int vpt, const RouteParams& rp, cudaStream_t st) {
+    const int grid = (rp.T + 7) / 8;
+    switch (vpt) {
+        case 1: route_kernel<1, MODE><<<grid, 256, 0, st>>>(rp); break;
+        case 2: route_kernel<2, MODE><<<grid, 256, 0, st>>>(rp); break;
+        case 4: route_kernel<4, MODE><<<grid, 256, 0, st>>>(rp); break;
+        case 8: route_kernel<8, MODE><<<grid, 256, 0, st>>>(rp); break;
+        default: route_kernel<16, MODE><<<grid, 256, 0, st>>>(rp); break;
+    }
+    return cudaGetLastError();
+}
+
+cudaError_t do_route(const b200moe_config& c, const RouteParams& rp, cudaStream_t st) {
+    const int vpt = c.num_experts / 32;
+    return c.routing_mode == B200MOE_ROUTING_DEEPSEEK ? launch_route<0>(vpt, rp, st) : launch_route<1>(vpt, rp, st);
+}
+
+#define CU_TRY(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) return (int)e_; } while (0)
+
+// Everything after routing: permute -> gather -> GEMM1 -> GEMM2 -> combine.
+int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
+                const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2, int T,
+                int local_offset, void* out, bool out_bf16, uint8_t* ws, const b200moe_ws_layout& L, cudaStream_t st) {
+    const b200moe_config& c = h->cfg;
+    const int El = c.num_local_experts, H = c.hidden, I = c.intermediate;
+    const int ntok = (int)L.token_tile, rows_cap = (int)L.rows_cap;
+    int* status = reinterpret_cast<int*>(ws + L.status);
+    int* counts = reinterpret_cast<int*>(ws + L.counts);
+    int* row0 = reinterpret_cast<int*>(ws + L.expert_row0);
+    int* tiles = reinterpret_cast<int*>(ws + L.tile_prefix);
+    int32_t* pair_row = reinterpret_cast<int32_t*>(ws + L.pair_row);
+    int32_t* row_token = reinterpret_cast<int32_t*>(ws + L.row_token);
+    float* row_w = reinterpret_cast<float*>(ws + L.row_w);
+    uint8_t* a_perm = ws + L.a_perm;
+    float* a_scale = reinterpret_cast<float*>(ws + L.a_scale_perm);
+    uint8_t* act_hi = ws + L.act_hi;
+    uint8_t* act_lo = ws + L.act_lo;
+    float* act_scale = reinterpret_cast<float*>(ws + L.act_scale);
+    float* y = reinterpret_cast<float*>(ws + L.y);
+
+    CUtensorMap m_w13, m_w2, m_a, m_hi, m_lo;
+    int rc;
+    if ((rc = make_map(&m_w13, w13, (uint64_t)El * 2 * I, H, 128))) return rc;
+    if ((rc = make_map(&m_w2, w2, (uint64_t)El * H, I, 128))) return rc;
+    if ((rc = make_map(&m_a, a_perm, rows_cap, H, ntok))) return rc;
+    if ((rc = make_map(&m_hi, act_hi, rows_cap, I, ntok))) return rc;
+    if ((rc = make_map(&m_lo, act_lo, rows_cap, I, ntok))) return rc;
+
+    PlanParams pp;
+    pp.T = T; pp.top_k = c.top_k; pp.num_local = El; pp.local_offset = local_offset; pp.token_tile = ntok;
+    pp.topk_idx = topk_idx; pp.topk_w = topk_w; pp.status = status; pp.counts = counts;
+    pp.expert_row0 = row0; pp.tile_prefix = tiles; pp.pair_row = pair_row; pp.row_token = row_token;
+    pp.row_w = row_w; pp.rows_cap = rows_cap;
+    permute_kernel<<<El, 256, 0, st>>>(pp);
+    CU_TRY(cudaGetLastError());
+
+    const long long max_rows = (long long)T * (c.top_k < El ? c.top_k : El) + (long long)ROW_ALIGN * El;
+    int ggrid = (int)((max_rows + 7) / 8);
+    if (ggrid > h->num_sms * 8) ggrid = h->num_sms * 8;
+    gather_kernel<<<ggrid, 256, 0, st>>>(static_cast<const uint8_t*>(hidden), static_cast<const float*>(hidden_scale),
+                                         row_token, status, a_perm, a_scale, T, H, rows_cap);
+    CU_TRY(cudaGetLastError());
+
+    GemmParams g1;
+    memset(&g1, 0, sizeof(g1));
+    g1.status = status; g1.counts = counts; g1.expert_row0 = row0; g1.tile_prefix = tiles; g1.num_local = El;
+    g1.KB = H / 128; g1.n_mtiles = I / 128; g1.rows_per_expert = 2 * I; g1.gate_offset = I; g1.scale_rows = 2 * I / 128;
+    g1.w_scale = static_cast<const float*>(s13); g1.b_scale = a_scale; g1.rows_cap = rows_cap;
+    g1.act_hi = act_hi; g1.act_lo = act_lo; g1.act_scale = act_scale; g1.I = I; g1.H = H;
+    g1.evict_first_weights = ntok < 128;
+    CU_TRY(launch_gemm_ntok<true>(ntok, h->num_sms, st, m_w13, m_a, m_a, g1));
+
+    GemmParams g2;
+    memset(&g2, 0, sizeof(g2));
+    g2.status = status; g2.counts = counts; g2.expert_row0 = row0; g2.tile_prefix = tiles; g2.num_local = El;
+    g2.KB = I / 128; g2.n_mtiles = H / 128; g2.rows_per_expert = H; g2.gate_offset = 0; g2.scale_rows = H / 128;
+    g2.w_scale = static_cast<const float*>(s2); g2.b_scale = act_scale; g2.rows_cap = rows_cap;
+    g2.row_w = row_w; g2.y = y; g2.H = H; g2.I = I;
+    g2.evict_first_weights = ntok < 128;
+    CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
+
+    const int cgrid = T < h->num_sms * 8 ? T : h->num_sms * 8;
+    if (out_bf16)
+        combine_kernel<true><<<cgrid, 256, 0, st>>>(y, topk_idx, pair_row, out, T, H, c.top_k, local_offset, El);
+    else
+        combine_kernel<false><<<cgrid, 256, 0, st>>>(y, topk_idx, pair_row, out, T, H, c.top_k, local_offset, El);
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
+int check_ws(b200moe_ctx* h, int T, void* ws, size_t ws_bytes, b200moe_ws_layout* L) {
+    layout(h->cfg, T, L);
+    if (!ws || ws_bytes < L->total_bytes || (reinterpret_cast<uintptr_t>(ws) & 255)) return B200MOE_E_WORKSPACE;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200moe_num_sms(void) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return n;
+}
+
+int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
+    if (!cfg || !out) return B200MOE_E_BADARG;
+    if (!cfg_ok(*cfg)) return B200MOE_E_BADARG;
+    int dev = 0;
+    CU_TRY(cudaGetDevice(&dev));
+    int major = 0, sms = 0;
+    CU_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    CU_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (major != 10) return B200MOE_E_DEVICE;
+    if (!get_encode()) return B200MOE_E_DRIVER;
+    CU_TRY((set_attr<16, true>()));  CU_TRY((set_attr<16, false>()));
+    CU_TRY((set_attr<32, true>()));  CU_TRY((set_attr<32, false>()));
+    CU_TRY((set_attr<64, true>()));  CU_TRY((set_attr<64, false>()));
+    CU_TRY((set_attr<128, true>())); CU_TRY((set_attr<128, false>()));
+    b200moe_ctx* h = new (std::nothrow) b200moe_ctx;
+    if (!h) return B200MOE_E_BADARG;
+    h->cfg = *cfg; h->device = dev; h->num_sms = sms;
+    *out = h;
+    return 0;
+}
+
+int b200moe_destroy(b200moe_handle h) {
+    if (!h) return B200MOE_E_BADARG;
+    delete h;
+    return 0;
+}
+
+int b200moe_workspace_layout(b200moe_handle h, int num_tokens, b200moe_ws_layout* L) {
+    if (!h || !L || num_tokens < 0) return B200MOE_E_BADARG;
+    layout(h->cfg, num_tokens, L);
+    return 0;
+}
+
+int b200moe_workspace_bytes(b200moe_handle h, int num_tokens, size_t* bytes) {
+    if (!h || !bytes || num_tokens < 0) return B200MOE_E_BADARG;
+    b200moe_ws_layout L;
+    layout(h->cfg, num_tokens, &L);
+    *bytes = L.total_bytes;
+    return 0;
+}
+
+int b200moe_launches_per_forward(b200moe_handle h, int num_tokens, int* launches) {
+    if (!h || !launches || num_tokens < 0) return B200MOE_E_BADARG;
+    *launches = num_tokens == 0 ? 0 : 6;   // route, permute, gather, gemm1, gemm2, combine
+    return 0;
+}
+
+int b200moe_route(b200moe_handle h, const void* logits, const void* bias, int T, float scale, int32_t* topk_idx,
+                  float* topk_w, void* stream) {
+    if (!h || T < 0) return B200MOE_E_BADARG;
+    if (T == 0) return 0;
+    if (!logits || !topk_idx || !topk_w) return B200MOE_E_BADARG;
+    const b200moe_config& c = h->cfg;
+    RouteParams rp;
+    rp.logits = static_cast<const float*>(logits); rp.bias = static_cast<const __nv_bfloat16*>(bias);
+    rp.T = T; rp.E = c.num_experts; rp.top_k = c.top_k; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
+    rp.local_offset = 0; rp.num_local = 0; rp.scale = scale; rp.topk_idx = topk_idx; rp.topk_w = topk_w;
+    rp.counts = nullptr;
+    CU_TRY(do_route(c, rp, static_cast<cudaStream_t>(stream)));
+    return 0;
+}
+
+int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, const void* hidden,
+                    const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2, int T,
+                    int local_offset, float scale, void* output, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+    if (!h || T < 0) return B200MOE_E_BADARG;
+    if (T == 0) return 0;
+    if (!logits || !hidden || !hidden_scale || !w13 || !s13 || !w2 || !s2 || !output) return B200MOE_E_BADARG;
+    b200moe_ws_layout L;
+    int rc = check_ws(h, T, workspace, workspace_bytes, &L);
+    if (rc) return rc;
+    const b200moe_config& c = h->cfg;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    // status + counts are contiguous at the head of the workspace: one memset clears both
+    CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
+    RouteParams rp;
+    rp.logits = static_cast<const float*>(logits); rp.bias = static_cast<const __nv_bfloat16*>(bias);
+    rp.T = T; rp.E = c.num_experts; rp.top_k = c.top_k; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
+    rp.local_offset = local_offset; rp.num_local = c.num_local_experts; rp.scale = scale;
+    rp.topk_idx = reinterpret_cast<int32_t*>(ws + L.topk_idx); rp.topk_w = reinterpret_cast<float*>(ws + L.topk_w);
+    rp.counts = reinterpret_cast<int*>(ws + L.counts);
+    CU_TRY(do_route(c, rp, st));
+    return run_experts(h, rp.topk_idx, rp.topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output,
+                       true, ws, L, st);
+}
+
+int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
+                           const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2,
+                           int T, int local_offset, float* output_f32, void* workspace, size_t workspace_bytes,
+                           void* stream) {
+    if (!h || T < 0) return B200MOE_E_BADARG;
+    if (T == 0) return 0;
+    if (!topk_idx || !topk_w || !hidden || !hidden_scale || !w13 || !s13 || !w2 || !s2 || !output_f32)
+        return B200MOE_E_BADARG;
+    b200moe_ws_layout L;
+    int rc = check_ws(h, T, workspace, workspace_bytes, &L);
+    if (rc) return rc;
+    const b200moe_config& c = h->cfg;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
+    const int n = T * c.top_k;
+    int grid = (n + 255) / 256;
+    if (grid > h->num_sms * 4) grid = h->num_sms * 4;
+    count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, local_offset, c.num_local_experts,
+                                       reinterpret_cast<int*>(ws + L.counts));
+    CU_TRY(cudaGetLastError());
+    return run_experts(h, topk_idx, topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output_f32,
+                       false, ws, L, st);
+}
+
+int b200moe_status(b200moe_handle h, const void* workspace, void* stream, int* word) {
+    if (!h || !workspace || !word) return B200MOE_E_BADARG;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    CU_TRY(cudaMemcpyAsync(word, workspace, sizeof(int), cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return *word ? B200MOE_E_KERNEL : 0;
+}
+
+const char* b200moe_strerror(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case B200MOE_E_BADARG: return "bad argument or unsupported shape";
+        case B200MOE_E_WORKSPACE: return "workspace too small or not 256-byte aligned";
+        case B200MOE_E_DRIVER: return "cuTensorMapEncodeTiled unavailable or failed";
+        case B200MOE_E_DEVICE: return "device is not compute capability 10.x";
+        case B200MOE_E_KERNEL: return "a kernel gave up a bounded wait or met a bad schedule (see status word)";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+    }
+}
+
+}  // extern "C"

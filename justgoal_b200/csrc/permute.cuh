@@ -1,0 +1,182 @@
+// Histogram / scan / permute / gather / combine kernels around the grouped GEMMs.
+//
+// Rows: every local (token, expert) pair gets one ROW in the expert-sorted buffers.  The rows
+// of one expert are contiguous, in ascending token order (a stable counting sort, so results
+// do not depend on atomic ordering), and each expert's segment starts on a multiple of
+// ROW_ALIGN rows so that per-tile scale vectors are 16-byte aligned for bulk copies.
+// The reference builds the same lists with atomics (expert order race-dependent):
+// kda05_reproduction_full_shape/fable-5.1/moe_fp8_fwd/<def>/fable51_moe_v94/kernel.cu:702-806,
+// goal_full_shape/fable-5.1/moe_fp8_fwd/<def>/moe_route.cuh:44-72.
+#pragma once
+#include <cuda_bf16.h>
+#include "common.cuh"
+
+namespace b200moe {
+
+constexpr int ROW_ALIGN = 16;
+constexpr int MAX_LOCAL = 256;
+
+// status word layout (int32[8]) at the head of the workspace
+enum : int { ST_ERR = 0, ST_PAIRS = 1, ST_ROWS = 2, ST_TILES = 3, ST_ACTIVE = 4 };
+
+struct PlanParams {
+    int T, top_k, num_local, local_offset, token_tile;
+    const int32_t* topk_idx;   // [T, top_k]
+    const float* topk_w;       // [T, top_k]
+    int* status;               // [8]
+    int* counts;               // [num_local]
+    int* expert_row0;          // [num_local + 1]
+    int* tile_prefix;          // [num_local + 1]
+    int32_t* pair_row;         // [T, top_k]
+    int32_t* row_token;        // [rows_cap]
+    float* row_w;              // [rows_cap]
+    int rows_cap;
+};
+
+// Counts per local expert from an explicit topk_idx (the expert-parallel receive side, where
+// routing ran on another rank).
+__global__ void count_kernel(const int32_t* __restrict__ topk_idx, int n, int local_offset, int num_local,
+                             int* __restrict__ counts) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int le = topk_idx[i] - local_offset;
+        if (le >= 0 && le < num_local) atomicAdd(counts + le, 1);
+    }
+}
+
+// One CTA per local expert.  Every CTA recomputes the (tiny) prefix over the counts, CTA 0
+// publishes it; then the CTA places its expert's pairs in token order.
+__global__ void __launch_bounds__(256) permute_kernel(const PlanParams p) {
+    __shared__ int s_row0[MAX_LOCAL + 1];
+    __shared__ int s_tiles[MAX_LOCAL + 1];
+    __shared__ int s_scan[256];
+    const int e = blockIdx.x, tid = threadIdx.x;
+
+    if (tid == 0) {
+        int rows = 0, tiles = 0, pairs = 0, active = 0;
+        for (int i = 0; i < p.num_local; ++i) {
+            const int c = p.counts[i];
+            s_row0[i] = rows; s_tiles[i] = tiles;
+            rows += (c + ROW_ALIGN - 1) / ROW_ALIGN * ROW_ALIGN;
+            tiles += (c + p.token_tile - 1) / p.token_tile;
+            pairs += c; active += c > 0;
+        }
+        s_row0[p.num_local] = rows; s_tiles[p.num_local] = tiles;
+        if (e == 0) {
+            p.status[ST_PAIRS] = pairs; p.status[ST_ROWS] = rows;
+            p.status[ST_TILES] = tiles; p.status[ST_ACTIVE] = active;
+        }
+    }
+    __syncthreads();
+    if (e == 0) {
+        for (int i = tid; i <= p.num_local; i += blockDim.x) {
+            p.expert_row0[i] = s_row0[i];
+            p.tile_prefix[i] = s_tiles[i];
+        }
+    }
+    const int cnt = p.counts[e];
+    const int row0 = s_row0[e];
+    const int row_end = s_row0[e + 1];
+    // padding rows of this segment carry token -1
+    for (int r = row0 + cnt + tid; r < row_end; r += blockDim.x) { p.row_token[r] = -1; p.row_w[r] = 0.f; }
+    if (cnt == 0) return;
+
+    // each thread owns a contiguous chunk of tokens -> order by token is preserved
+    const int ge = e + p.local_offset;
+    const int chunk = (p.T + blockDim.x - 1) / blockDim.x;
+    const int t0 = min(tid * chunk, p.T), t1 = min(t0 + chunk, p.T);
+    int mine = 0;
+    for (int t = t0; t < t1; ++t)
+        for (int k = 0; k < p.top_k; ++k) mine += (p.topk_idx[(size_t)t * p.top_k + k] == ge);
+    s_scan[tid] = mine;
+    __syncthreads();
+    // inclusive Hillis-Steele scan over 256 counters
+    for (int off = 1; off < 256; off <<= 1) {
+        const int add = tid >= off ? s_scan[tid - off] : 0;
+        __syncthreads();
+        s_scan[tid] += add;
+        __syncthreads();
+    }
+    int r = row0 + s_scan[tid] - mine;
+    for (int t = t0; t < t1; ++t)
+        for (int k = 0; k < p.top_k; ++k) {
+            const size_t i = (size_t)t * p.top_k + k;
+            if (p.topk_idx[i] == ge) {
+                p.pair_row[i] = r;
+                p.row_token[r] = t;
+                p.row_w[r] = p.topk_w[i];
+                ++r;
+            }
+        }
+}
+
+// Expert-sorted copy of the fp8 activations and of their scales: a_perm[row] = hidden[token],
+// a_scale_perm[kb][row] = hidden_scale[kb][token].  One warp per row, grid-stride.
+__global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__ hidden, const float* __restrict__ hscale,
+                                                     const int32_t* __restrict__ row_token, const int* __restrict__ status,
+                                                     uint8_t* __restrict__ a_perm, float* __restrict__ a_scale_perm,
+                                                     int T, int H, int rows_cap) {
+    const int rows = status[ST_ROWS];
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int KB = H >> 7;
+    for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+        const int t = row_token[r];
+        uint4* dst = reinterpret_cast<uint4*>(a_perm + (size_t)r * H);
+        if (t < 0) {   // padding row: finite zeros so that no NaN pattern reaches the tensor core
+            for (int i = lane; i < H / 16; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+            for (int kb = lane; kb < KB; kb += 32) a_scale_perm[(size_t)kb * rows_cap + r] = 0.f;
+            continue;
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * H);
+        for (int i = lane; i < H / 16; i += 32) dst[i] = __ldg(src + i);
+        for (int kb = lane; kb < KB; kb += 32) a_scale_perm[(size_t)kb * rows_cap + r] = __ldg(hscale + (size_t)kb * T + t);
+    }
+}
+
+// out[t, :] = sum over the token's local pairs (ascending expert order = the order they were
+// placed in topk rows is NOT sorted, so sort the <= 8 rows by row index, which is expert
+// order) of y[row, :]; fp32 accumulation, one rounding.  Tokens without a local pair get zeros.
+template <bool OUT_BF16>
+__global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ topk_idx,
+                                                      const int32_t* __restrict__ pair_row, void* __restrict__ out,
+                                                      int T, int H, int top_k, int local_offset, int num_local) {
+    __shared__ int s_rows[8];
+    __shared__ int s_n;
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int n = 0;
+            for (int k = 0; k < top_k; ++k) {
+                const int le = topk_idx[(size_t)t * top_k + k] - local_offset;
+                if (le >= 0 && le < num_local) {
+                    const int r = pair_row[(size_t)t * top_k + k];
+                    int j = n++;
+                    while (j > 0 && s_rows[j - 1] > r) { s_rows[j] = s_rows[j - 1]; --j; }
+                    s_rows[j] = r;
+                }
+            }
+            s_n = n;
+        }
+        __syncthreads();
+        const int n = s_n;
+        for (int h = threadIdx.x * 4; h < H; h += blockDim.x * 4) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < n; ++j) {
+                const float4 v = *reinterpret_cast<const float4*>(y + (size_t)s_rows[j] * H + h);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            if (OUT_BF16) {
+                __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y);
+                __nv_bfloat162 b = __floats2bfloat162_rn(acc.z, acc.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&a);
+                pk.y = *reinterpret_cast<uint32_t*>(&b);
+                *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)t * H + h) = pk;
+            } else {
+                *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (size_t)t * H + h) = acc;
+            }
+        }
+    }
+}
+
+}  // namespace b200moe

@@ -1,0 +1,208 @@
+"""Operator entry point with the reference's signature.
+
+`run(...)` keeps the argument list, dtypes, layouts and return value of the reference
+solutions' `main.py::run` (goal_full_shape/fable-5.1/moe_fp8_fwd/<def>/main.py:102-117,
+non destination-passing) and `run_dps(..., output)` the destination-passing twin
+(kda05_reproduction_full_shape/fable-5.1/moe_fp8_fwd/<def>/fable51_moe_v94/main.py:196-209).
+All work happens in libb200moe.so through its C ABI on the caller's current CUDA stream;
+torch is only used for tensors, the stream handle and the workspace allocation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .inputs import MoEShape, ROUTING_DS, ROUTING_RENORM_NAIVE  # noqa: F401
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _contig(t):
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _scalar(v, kind):
+    if isinstance(v, torch.Tensor):
+        v = v.item()
+    return kind(v)
+
+
+class MoELayer:
+    """One rank's share of an MoE layer of a fixed shape: a library handle plus workspaces
+    cached per token count (the reference caches per (T, device): GF main.py:68-94)."""
+
+    def __init__(self, shape: MoEShape, device=None):
+        if not torch.cuda.is_available():
+            raise _lib.B200MoEError("b200moe needs a CUDA device (no CPU fallback exists)")
+        self.shape = shape
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        cfg = _lib.Config(shape.hidden, shape.intermediate, shape.num_experts, shape.num_local_experts,
+                          shape.top_k, shape.n_group, shape.topk_group, shape.routing_mode)
+        self._h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib.b200moe_create(C.byref(cfg), C.byref(self._h)), "b200moe_create")
+        self._ws = {}
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            _lib.lib.b200moe_destroy(h)
+            self._h = None
+
+    # ------------------------------------------------------------------ workspace
+    def workspace(self, T: int) -> torch.Tensor:
+        ws = self._ws.get(T)
+        if ws is None:
+            n = C.c_size_t()
+            _lib.check(_lib.lib.b200moe_workspace_bytes(self._h, T, C.byref(n)), "b200moe_workspace_bytes")
+            ws = torch.empty(max(int(n.value), 256), dtype=torch.uint8, device=self.device)
+            assert ws.data_ptr() % 256 == 0
+            self._ws[T] = ws
+        return ws
+
+    def layout(self, T: int) -> _lib.WsLayout:
+        L = _lib.WsLayout()
+        _lib.check(_lib.lib.b200moe_workspace_layout(self._h, T, C.byref(L)), "b200moe_workspace_layout")
+        return L
+
+    def view(self, T: int, name: str, dtype, shape):
+        """A typed view of one intermediate buffer of the workspace (tests / debugging)."""
+        L = self.layout(T)
+        off = getattr(L, name)
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        return self.workspace(T)[off:off + nbytes].view(dtype).view(*shape)
+
+    def launches_per_forward(self, T: int) -> int:
+        n = C.c_int()
+        _lib.check(_lib.lib.b200moe_launches_per_forward(self._h, T, C.byref(n)))
+        return int(n.value)
+
+    def status(self, T: int) -> int:
+        word = C.c_int(0)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = _lib.lib.b200moe_status(self._h, _ptr(self.workspace(T)), C.c_void_p(stream), C.byref(word))
+        if rc not in (0, -5):
+            _lib.check(rc, "b200moe_status")
+        return int(word.value)
+
+    # ------------------------------------------------------------------ operator
+    def forward(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                routed_scaling_factor, output=None):
+        s = self.shape
+        T = int(hidden_states.shape[0])
+        self._check(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                    gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, T)
+        if output is None:
+            output = torch.empty(T, s.hidden, dtype=torch.bfloat16, device=hidden_states.device)
+        elif output.shape != (T, s.hidden) or output.dtype != torch.bfloat16 or not output.is_contiguous():
+            raise ValueError("output must be a contiguous bf16 [T, hidden] tensor")
+        if T == 0:
+            return output
+        ws = self.workspace(T)
+        tensors = [_contig(t) if t is not None else None for t in (
+            routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+            gemm1_weights_scale, gemm2_weights, gemm2_weights_scale)]
+        stream = torch.cuda.current_stream(hidden_states.device).cuda_stream
+        rc = _lib.lib.b200moe_forward(self._h, *[_ptr(t) for t in tensors], T,
+                                      _scalar(local_expert_offset, int), _scalar(routed_scaling_factor, float),
+                                      _ptr(output), _ptr(ws), ws.numel(), C.c_void_p(stream))
+        _lib.check(rc, "b200moe_forward")
+        return output
+
+    def forward_routed(self, topk_idx, topk_w, hidden_states, hidden_states_scale, gemm1_weights,
+                       gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset, output=None):
+        """Expert part only, fp32 output (sum over the local experts, no bf16 rounding)."""
+        s = self.shape
+        T = int(hidden_states.shape[0])
+        if output is None:
+            output = torch.empty(T, s.hidden, dtype=torch.float32, device=hidden_states.device)
+        if T == 0:
+            return output
+        if topk_idx.dtype != torch.int32 or topk_w.dtype != torch.float32:
+            raise ValueError("topk_idx must be int32 and topk_w float32")
+        ws = self.workspace(T)
+        tensors = [_contig(t) for t in (topk_idx, topk_w, hidden_states, hidden_states_scale, gemm1_weights,
+                                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale)]
+        stream = torch.cuda.current_stream(hidden_states.device).cuda_stream
+        rc = _lib.lib.b200moe_forward_routed(self._h, *[_ptr(t) for t in tensors], T,
+                                             _scalar(local_expert_offset, int), _ptr(output), _ptr(ws),
+                                             ws.numel(), C.c_void_p(stream))
+        _lib.check(rc, "b200moe_forward_routed")
+        return output
+
+    def route(self, routing_logits, routing_bias, routed_scaling_factor):
+        s = self.shape
+        T = int(routing_logits.shape[0])
+        idx = torch.empty(T, s.top_k, dtype=torch.int32, device=routing_logits.device)
+        w = torch.empty(T, s.top_k, dtype=torch.float32, device=routing_logits.device)
+        if T:
+            stream = torch.cuda.current_stream(routing_logits.device).cuda_stream
+            rb = None if routing_bias is None else _contig(routing_bias)
+            rc = _lib.lib.b200moe_route(self._h, _ptr(_contig(routing_logits)), _ptr(rb), T,
+                                        _scalar(routed_scaling_factor, float), _ptr(idx), _ptr(w),
+                                        C.c_void_p(stream))
+            _lib.check(rc, "b200moe_route")
+        return idx, w
+
+    def _check(self, logits, bias, hs, hss, w13, s13, w2, s2, T):
+        s = self.shape
+        H, I, E, El = s.hidden, s.intermediate, s.num_experts, s.num_local_experts
+        f8 = torch.float8_e4m3fn
+        want = [("routing_logits", logits, (T, E), torch.float32),
+                ("hidden_states", hs, (T, H), f8),
+                ("hidden_states_scale", hss, (H // 128, T), torch.float32),
+                ("gemm1_weights", w13, (El, 2 * I, H), f8),
+                ("gemm1_weights_scale", s13, (El, 2 * I // 128, H // 128), torch.float32),
+                ("gemm2_weights", w2, (El, H, I), f8),
+                ("gemm2_weights_scale", s2, (El, H // 128, I // 128), torch.float32)]
+        if bias is not None:
+            want.append(("routing_bias", bias, (E,), torch.bfloat16))
+        for name, t, shape, dt in want:
+            if tuple(t.shape) != shape or t.dtype != dt:
+                raise ValueError(f"{name}: expected {dt} {shape}, got {t.dtype} {tuple(t.shape)}")
+            if not t.is_cuda:
+                raise ValueError(f"{name} must be a CUDA tensor")
+
+
+_layers = {}
+
+
+def _layer_for(routing_logits, hidden_states, gemm1_weights, top_k=8, n_group=8, topk_group=4,
+               routing_mode=ROUTING_DS) -> MoELayer:
+    shape = MoEShape(hidden=int(hidden_states.shape[1]), intermediate=int(gemm1_weights.shape[1]) // 2,
+                     num_experts=int(routing_logits.shape[1]), num_local_experts=int(gemm1_weights.shape[0]),
+                     top_k=top_k, n_group=n_group, topk_group=topk_group, routing_mode=routing_mode)
+    key = (shape, hidden_states.device.index)
+    layer = _layers.get(key)
+    if layer is None:
+        layer = _layers[key] = MoELayer(shape, hidden_states.device)
+    return layer
+
+
+@torch.no_grad()
+def run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+        gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor):
+    """DeepSeek-V3 routing (top-8 of 8 groups, 4 groups kept), returns bf16 [T, hidden]."""
+    layer = _layer_for(routing_logits, hidden_states, gemm1_weights)
+    return layer.forward(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                         gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                         routed_scaling_factor)
+
+
+@torch.no_grad()
+def run_dps(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+            gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, output):
+    """Destination-passing twin of `run`: writes into `output` and returns it."""
+    layer = _layer_for(routing_logits, hidden_states, gemm1_weights)
+    return layer.forward(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                         gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                         routed_scaling_factor, output=output)

@@ -1,0 +1,136 @@
+"""GPU: the whole operator through the C ABI against the oracle and the golden vectors.
+
+Output tolerance (stated for the operator): |got - want| <= 1e-2 + 1e-2*|want| elementwise on
+the bf16 output; the fraction of failing elements must be 0.  Integer work (expert lists,
+row maps) is compared exactly."""
+import numpy as np
+import pytest
+import torch
+
+import util
+from util import I, O
+
+pytestmark = pytest.mark.gpu
+
+
+def _layer(shape):
+    from justgoal_b200 import MoELayer
+    return MoELayer(shape)
+
+
+def _run(shape, d):
+    layer = _layer(shape)
+    out = layer.forward(*util.op_args(util.to_cuda(d)))
+    torch.cuda.synchronize()
+    T = d["hidden_states"].shape[0]
+    assert layer.status(T) == 0
+    return layer, out
+
+
+def _assert_close(out, want_bf16, what):
+    rep = O.compare_output(out, want_bf16, util.ATOL, util.RTOL)
+    assert rep["finite"], (what, rep)
+    assert rep["fail_frac"] == 0.0, (what, rep)
+    return rep
+
+
+@pytest.mark.parametrize("name", ["tiny_ds_t33", "tiny_ds_t7_off16", "tiny_renorm_t20", "ds_v3_t16"])
+def test_layer_matches_golden_and_oracle(name):
+    shape, d, g = util.golden_case(name)
+    layer, out = _run(shape, d)
+    golden = torch.from_numpy(g["output_bf16_bits"]).view(torch.bfloat16)
+    _assert_close(out, golden, name + " vs golden")
+    r = util.run_oracle(shape, d)
+    _assert_close(out, r.output, name + " vs oracle")
+    # tokens without a local expert must be exact zeros
+    off, El = d["local_expert_offset"], shape.num_local_experts
+    local = ((r.topk_idx >= off) & (r.topk_idx < off + El)).any(dim=1)
+    assert bool((out.cpu()[~local].float() == 0).all())
+
+
+def test_permute_tables_and_intermediates():
+    """Integer structures exactly; the re-quantised SwiGLU output within e4m3 hi+lo precision."""
+    shape, d, g = util.golden_case("tiny_ds_t33")
+    T, K, El = 33, shape.top_k, shape.num_local_experts
+    layer, out = _run(shape, d)
+    r = util.run_oracle(shape, d, keep_inter=True)
+    L = layer.layout(T)
+    rows_cap = int(L.rows_cap)
+    counts = layer.view(T, "counts", torch.int32, (El,)).cpu()
+    row0 = layer.view(T, "expert_row0", torch.int32, (El + 1,)).cpu()
+    row_token = layer.view(T, "row_token", torch.int32, (rows_cap,)).cpu()
+    status = layer.view(T, "status", torch.int32, (8,)).cpu()
+    want_counts = torch.tensor([len(r.expert_tokens.get(e, [])) for e in range(El)], dtype=torch.int32)
+    assert torch.equal(counts, want_counts)
+    assert int(status[1]) == int(want_counts.sum())
+    assert int(status[4]) == int((want_counts > 0).sum())
+    for e in range(El):
+        assert int(row0[e]) % 16 == 0
+        assert int(row0[e + 1]) - int(row0[e]) == (int(counts[e]) + 15) // 16 * 16
+        toks = row_token[int(row0[e]):int(row0[e]) + int(counts[e])]
+        if int(counts[e]):
+            assert torch.equal(toks.long(), r.expert_tokens[e])          # stable: ascending tokens
+        pad = row_token[int(row0[e]) + int(counts[e]):int(row0[e + 1])]
+        assert bool((pad == -1).all())
+    # SwiGLU output, de-quantised (hi + lo) * scale, against the oracle's fp32 C
+    Iz = shape.intermediate
+    hi = layer.view(T, "act_hi", torch.float8_e4m3fn, (rows_cap, Iz)).cpu().float()
+    lo = layer.view(T, "act_lo", torch.float8_e4m3fn, (rows_cap, Iz)).cpu().float()
+    sc = layer.view(T, "act_scale", torch.float32, (Iz // 128, rows_cap)).cpu()
+    for e, toks in r.expert_tokens.items():
+        rows = slice(int(row0[e]), int(row0[e]) + len(toks))
+        deq = (hi[rows] + lo[rows]) * sc[:, rows].t().repeat_interleave(128, dim=1)
+        C = r.inter[e][1]
+        err = (deq - C).abs().max().item()
+        assert err <= 2e-3 * C.abs().max().item() + 1e-6, (e, err)
+
+
+def test_edge_cases():
+    from justgoal_b200 import MoELayer
+    shape = I.TINY_DS
+    layer = MoELayer(shape)
+    # T == 0 -> empty output
+    d = util.to_cuda(I.make_inputs(shape, 0, seed=4))
+    out = layer.forward(*util.op_args(d))
+    assert out.shape == (0, shape.hidden)
+    # no token routed to a local expert -> all zeros (offset far outside the expert range)
+    d = I.make_inputs(shape, 9, seed=5)
+    d["local_expert_offset"] = 4096
+    out = layer.forward(*util.op_args(util.to_cuda(d)))
+    torch.cuda.synchronize()
+    assert bool((out.float() == 0).all())
+    # routing_bias None == zeros; scalars as 0-d tensors; destination-passing form
+    d = I.make_inputs(shape, 12, seed=6)
+    dz = dict(d); dz["routing_bias"] = torch.zeros_like(d["routing_bias"])
+    want = util.run_oracle(shape, dz).output
+    dc = util.to_cuda(d)
+    dc["routing_bias"] = None
+    dc["local_expert_offset"] = torch.tensor(0)
+    dc["routed_scaling_factor"] = torch.tensor(2.5)
+    dst = torch.full((12, shape.hidden), 7.0, dtype=torch.bfloat16, device="cuda")
+    got = layer.forward(*util.op_args(dc), output=dst)
+    torch.cuda.synchronize()
+    assert got.data_ptr() == dst.data_ptr()
+    assert O.compare_output(got, want, util.ATOL, util.RTOL)["fail_frac"] == 0.0
+
+
+def test_poisoned_workspace_gives_same_result():
+    """Nothing may be read from the workspace before it is written in the same call."""
+    shape, d, g = util.golden_case("tiny_ds_t33")
+    layer, out1 = _run(shape, d)
+    out1 = out1.clone()
+    layer.workspace(33).fill_(0xFF)
+    out2 = layer.forward(*util.op_args(util.to_cuda(d)))
+    torch.cuda.synchronize()
+    assert torch.equal(out1.view(torch.int16), out2.view(torch.int16))   # also: run-to-run determinism
+
+
+def test_reference_entry_point_signature():
+    """`run(...)` with the reference's ten positional arguments on the reference shape."""
+    from justgoal_b200 import run
+    shape, d, g = util.golden_case("ds_v3_t16")
+    out = run(*util.op_args(util.to_cuda(d)))
+    torch.cuda.synchronize()
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == (16, 7168)
+    golden = torch.from_numpy(g["output_bf16_bits"]).view(torch.bfloat16)
+    _assert_close(out, golden, "run() vs golden")
