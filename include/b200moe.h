@@ -134,6 +134,16 @@ int b200moe_status(b200moe_handle h, const void* workspace, void* cuda_stream, i
  * launches, not of kernels that do useful work). */
 int b200moe_launches_per_forward(b200moe_handle h, int num_tokens, int* launches);
 
+/* Optional stage timing.  enable(slots > 0) creates slots x 7 CUDA events; every forward then
+ * records them around its six kernels (slot = call number modulo slots); enable(0) turns it
+ * off.  read(slot) waits for that call's last event and writes six durations in
+ * milliseconds: route (or count), permute, gather, gemm1, gemm2, combine.  Counterpart of
+ * the reference's in-kernel time stamps and pybind timing getters
+ * (goal_full_shape/fable-5.1/moe_fp8_fwd/<def>/moe_small.cuh:55-60,
+ *  kda05_reproduction_single_shape/fable-5.1/moe_fp8_fwd/t14107/moe_kernel.cu:2966-3009). */
+int b200moe_profile_enable(b200moe_handle h, int slots);
+int b200moe_profile_read(b200moe_handle h, int slot, float* stage_ms);
+
 const char* b200moe_strerror(int code);
 int b200moe_num_sms(void);            /* cf. `moe_num_sms`, SF1/kernel.py:40-44 */
 

@@ -40,11 +40,14 @@ def _load():
     lib.b200moe_forward_routed.argtypes = [vp, vp, vp] + [vp] * 6 + [i, i, vp, vp, sz, vp]
     lib.b200moe_status.argtypes = [vp, vp, vp, C.POINTER(i)]
     lib.b200moe_launches_per_forward.argtypes = [vp, i, C.POINTER(i)]
+    lib.b200moe_profile_enable.argtypes = [vp, i]
+    lib.b200moe_profile_read.argtypes = [vp, i, C.POINTER(f)]
     lib.b200moe_strerror.argtypes = [i]
     lib.b200moe_strerror.restype = C.c_char_p
     lib.b200moe_num_sms.argtypes = []
     for name in ("create", "destroy", "workspace_bytes", "workspace_layout", "forward", "route",
-                 "forward_routed", "status", "launches_per_forward", "num_sms"):
+                 "forward_routed", "status", "launches_per_forward", "num_sms", "profile_enable",
+                 "profile_read"):
         getattr(lib, "b200moe_" + name).restype = i
     return lib
 

@@ -20,10 +20,15 @@
 
 using namespace b200moe;
 
+constexpr int PROF_POINTS = 7;   // before route, after route, permute, gather, gemm1, gemm2, combine
+
 struct b200moe_ctx {
     b200moe_config cfg;
     int device;
     int num_sms;
+    int prof_slots;            // 0 = profiling off
+    long long prof_calls;      // forwards recorded since profiling was enabled
+    cudaEvent_t* prof_events;  // [prof_slots][PROF_POINTS]
 };
 
 namespace {
@@ -169,6 +174,13 @@ cudaError_t do_route(const b200moe_config& c, const RouteParams& rp, cudaStream_
 
 #define CU_TRY(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) return (int)e_; } while (0)
 
+// Optional per-stage CUDA events (b200moe_profile_enable): point k of the current slot.
+inline cudaError_t prof_mark(b200moe_ctx* h, int point, cudaStream_t st) {
+    if (!h->prof_slots) return cudaSuccess;
+    const long long slot = h->prof_calls % h->prof_slots;
+    return cudaEventRecord(h->prof_events[slot * PROF_POINTS + point], st);
+}
+
 // Everything after routing: permute -> gather -> GEMM1 -> GEMM2 -> combine.
 int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
                 const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2, int T,
@@ -205,6 +217,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     pp.row_w = row_w; pp.rows_cap = rows_cap;
     permute_kernel<<<El, 256, 0, st>>>(pp);
     CU_TRY(cudaGetLastError());
+    CU_TRY(prof_mark(h, 2, st));
 
     const long long max_rows = (long long)T * (c.top_k < El ? c.top_k : El) + (long long)ROW_ALIGN * El;
     int ggrid = (int)((max_rows + 7) / 8);
@@ -212,6 +225,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     gather_kernel<<<ggrid, 256, 0, st>>>(static_cast<const uint8_t*>(hidden), static_cast<const float*>(hidden_scale),
                                          row_token, status, a_perm, a_scale, T, H, rows_cap);
     CU_TRY(cudaGetLastError());
+    CU_TRY(prof_mark(h, 3, st));
 
     GemmParams g1;
     memset(&g1, 0, sizeof(g1));
@@ -221,6 +235,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g1.act_hi = act_hi; g1.act_lo = act_lo; g1.act_scale = act_scale; g1.I = I; g1.H = H;
     g1.evict_first_weights = ntok < 128;
     CU_TRY(launch_gemm_ntok<true>(ntok, h->num_sms, st, m_w13, m_a, m_a, g1));
+    CU_TRY(prof_mark(h, 4, st));
 
     GemmParams g2;
     memset(&g2, 0, sizeof(g2));
@@ -230,6 +245,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g2.row_w = row_w; g2.y = y; g2.H = H; g2.I = I;
     g2.evict_first_weights = ntok < 128;
     CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
+    CU_TRY(prof_mark(h, 5, st));
 
     const int cgrid = T < h->num_sms * 8 ? T : h->num_sms * 8;
     if (out_bf16)
@@ -237,6 +253,8 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     else
         combine_kernel<false><<<cgrid, 256, 0, st>>>(y, topk_idx, pair_row, out, T, H, c.top_k, local_offset, El);
     CU_TRY(cudaGetLastError());
+    CU_TRY(prof_mark(h, 6, st));
+    if (h->prof_slots) ++h->prof_calls;
     return 0;
 }
 
@@ -274,13 +292,40 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     b200moe_ctx* h = new (std::nothrow) b200moe_ctx;
     if (!h) return B200MOE_E_BADARG;
     h->cfg = *cfg; h->device = dev; h->num_sms = sms;
+    h->prof_slots = 0; h->prof_calls = 0; h->prof_events = nullptr;
     *out = h;
     return 0;
 }
 
 int b200moe_destroy(b200moe_handle h) {
     if (!h) return B200MOE_E_BADARG;
+    b200moe_profile_enable(h, 0);
     delete h;
+    return 0;
+}
+
+int b200moe_profile_enable(b200moe_handle h, int slots) {
+    if (!h || slots < 0) return B200MOE_E_BADARG;
+    if (h->prof_events) {
+        for (int i = 0; i < h->prof_slots * PROF_POINTS; ++i) cudaEventDestroy(h->prof_events[i]);
+        delete[] h->prof_events;
+        h->prof_events = nullptr;
+    }
+    h->prof_slots = 0; h->prof_calls = 0;
+    if (slots == 0) return 0;
+    h->prof_events = new (std::nothrow) cudaEvent_t[(size_t)slots * PROF_POINTS];
+    if (!h->prof_events) return B200MOE_E_BADARG;
+    for (int i = 0; i < slots * PROF_POINTS; ++i) CU_TRY(cudaEventCreate(&h->prof_events[i]));
+    h->prof_slots = slots;
+    return 0;
+}
+
+int b200moe_profile_read(b200moe_handle h, int slot, float* stage_ms) {
+    if (!h || !stage_ms || !h->prof_slots || slot < 0 || slot >= h->prof_slots || slot >= h->prof_calls)
+        return B200MOE_E_BADARG;
+    cudaEvent_t* ev = h->prof_events + (size_t)slot * PROF_POINTS;
+    CU_TRY(cudaEventSynchronize(ev[PROF_POINTS - 1]));
+    for (int i = 0; i + 1 < PROF_POINTS; ++i) CU_TRY(cudaEventElapsedTime(stage_ms + i, ev[i], ev[i + 1]));
     return 0;
 }
 
@@ -334,6 +379,7 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     // status + counts are contiguous at the head of the workspace: one memset clears both
     CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
+    CU_TRY(prof_mark(h, 0, st));
     RouteParams rp;
     rp.logits = static_cast<const float*>(logits); rp.bias = static_cast<const __nv_bfloat16*>(bias);
     rp.T = T; rp.E = c.num_experts; rp.top_k = c.top_k; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
@@ -341,6 +387,7 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     rp.topk_idx = reinterpret_cast<int32_t*>(ws + L.topk_idx); rp.topk_w = reinterpret_cast<float*>(ws + L.topk_w);
     rp.counts = reinterpret_cast<int*>(ws + L.counts);
     CU_TRY(do_route(c, rp, st));
+    CU_TRY(prof_mark(h, 1, st));
     return run_experts(h, rp.topk_idx, rp.topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output,
                        true, ws, L, st);
 }
@@ -360,12 +407,14 @@ int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const floa
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
+    CU_TRY(prof_mark(h, 0, st));
     const int n = T * c.top_k;
     int grid = (n + 255) / 256;
     if (grid > h->num_sms * 4) grid = h->num_sms * 4;
     count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, local_offset, c.num_local_experts,
                                        reinterpret_cast<int*>(ws + L.counts));
     CU_TRY(cudaGetLastError());
+    CU_TRY(prof_mark(h, 1, st));
     return run_experts(h, topk_idx, topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output_f32,
                        false, ws, L, st);
 }

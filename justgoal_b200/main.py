@@ -85,6 +85,16 @@ class MoELayer:
         _lib.check(_lib.lib.b200moe_launches_per_forward(self._h, T, C.byref(n)))
         return int(n.value)
 
+    STAGES = ("route", "permute", "gather", "gemm1", "gemm2", "combine")
+
+    def profile_enable(self, slots: int):
+        _lib.check(_lib.lib.b200moe_profile_enable(self._h, int(slots)), "b200moe_profile_enable")
+
+    def profile_read(self, slot: int) -> dict:
+        ms = (C.c_float * 6)()
+        _lib.check(_lib.lib.b200moe_profile_read(self._h, int(slot), ms), "b200moe_profile_read")
+        return dict(zip(self.STAGES, [float(x) for x in ms]))
+
     def status(self, T: int) -> int:
         word = C.c_int(0)
         stream = torch.cuda.current_stream(self.device).cuda_stream
