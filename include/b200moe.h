@@ -32,6 +32,9 @@ extern "C" {
 #define B200MOE_E_DRIVER   (-3)   /* cuTensorMapEncodeTiled unavailable / failed           */
 #define B200MOE_E_DEVICE   (-4)   /* not an sm_100 device                                  */
 #define B200MOE_E_KERNEL   (-5)   /* a kernel recorded a device-side error (see status)    */
+#define B200MOE_E_TOO_LARGE (-6)  /* more tokens than the allocation-free entry point holds */
+
+#define B200MOE_NOALLOC_MAX_TOKENS 8192
 
 typedef struct b200moe_config {
     int hidden;              /* H, multiple of 128                                         */
@@ -123,6 +126,34 @@ int b200moe_forward_routed(b200moe_handle h,
                            int num_tokens, int local_expert_offset,
                            float* output_f32, void* workspace, size_t workspace_bytes,
                            void* cuda_stream);
+
+/* Expert-sorted row map without any workspace from the caller.  (No counterpart in the
+ * reference: its launchers always receive caller-allocated workspaces.)
+ *
+ * Some hosts of this library cannot allocate device memory at the point where they need the
+ * permutation: a serving loop that runs under a fixed memory budget with its allocator frozen
+ * after start-up, a plugin called from a runtime that owns all device memory, or code that
+ * sits between stream operations where a cudaMalloc would stall the device.  For them this
+ * entry point does the histogram / scan / permute step (the same kernels b200moe_forward uses)
+ * with its scratch -- histogram counters, tile prefix, status words and the token->row map --
+ * in a fixed array inside the library image (about 260 KB per GPU that loads the library, held
+ * until the process exits).  It calls no cudaMalloc/cudaFree and no allocating routine.
+ *
+ *   in : topk_idx int32 [T, top_k], topk_w float [T, top_k], local_expert_offset
+ *   out: expert_row0 int32 [E_local + 1]   first (16-aligned) row of each local expert
+ *        row_token   int32 [rows_capacity] token of each row, -1 for the padding of a segment
+ *        row_w       float [rows_capacity] routing weight of each row
+ *   rows_capacity must be at least b200moe_ws_layout.rows_cap for this T.
+ *
+ * Limits and rules: T <= B200MOE_NOALLOC_MAX_TOKENS, else B200MOE_E_TOO_LARGE.  The first call
+ * on a device looks up the array's device address (once per device); make that first call
+ * outside any stream capture.  All calls on a device share the one array: it is cleared at the
+ * start of every call, and two calls that overlap on the GPU (different streams, no ordering
+ * between them) race -- serialise them. */
+int b200moe_permute_noalloc(b200moe_handle h, const int32_t* topk_idx, const float* topk_w,
+                            int num_tokens, int local_expert_offset,
+                            int32_t* expert_row0, int32_t* row_token, float* row_w,
+                            int rows_capacity, void* cuda_stream);
 
 /* Synchronises the stream, reads the device error word of the last forward on this
  * workspace into *word (0 = no error) and returns B200MOE_E_KERNEL if it is non-zero.

@@ -40,6 +40,7 @@ def _load():
     lib.b200moe_forward_routed.argtypes = [vp, vp, vp] + [vp] * 6 + [i, i, vp, vp, sz, vp]
     lib.b200moe_status.argtypes = [vp, vp, vp, C.POINTER(i)]
     lib.b200moe_launches_per_forward.argtypes = [vp, i, C.POINTER(i)]
+    lib.b200moe_permute_noalloc.argtypes = [vp, vp, vp, i, i, vp, vp, vp, i, vp]
     lib.b200moe_profile_enable.argtypes = [vp, i]
     lib.b200moe_profile_read.argtypes = [vp, i, C.POINTER(f)]
     lib.b200moe_strerror.argtypes = [i]
@@ -47,10 +48,12 @@ def _load():
     lib.b200moe_num_sms.argtypes = []
     for name in ("create", "destroy", "workspace_bytes", "workspace_layout", "forward", "route",
                  "forward_routed", "status", "launches_per_forward", "num_sms", "profile_enable",
-                 "profile_read"):
+                 "profile_read", "permute_noalloc"):
         getattr(lib, "b200moe_" + name).restype = i
     return lib
 
+
+NOALLOC_MAX_TOKENS = 8192   # B200MOE_NOALLOC_MAX_TOKENS in include/b200moe.h
 
 lib = _load()
 

@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 
 #include "../../include/b200moe.h"
@@ -75,7 +76,7 @@ int pick_token_tile(const b200moe_config& c, int T) {
     return 128;
 }
 
-int rows_capacity(const b200moe_config& c, int T) {
+int rows_capacity_for(const b200moe_config& c, int T) {
     const long long per_tok = c.top_k < c.num_local_experts ? c.top_k : c.num_local_experts;
     long long rows = (long long)T * per_tok + (long long)ROW_ALIGN * c.num_local_experts;
     rows = (rows + 127) / 128 * 128 + 128;
@@ -85,7 +86,7 @@ int rows_capacity(const b200moe_config& c, int T) {
 void layout(const b200moe_config& c, int T, b200moe_ws_layout* L) {
     const size_t A = 256;
     const int El = c.num_local_experts, K = c.top_k;
-    const size_t rows = (size_t)rows_capacity(c, T);
+    const size_t rows = (size_t)rows_capacity_for(c, T);
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, A); return o; };
     L->status = take(8 * 4);
@@ -258,6 +259,16 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     return 0;
 }
 
+// ---- scratch of b200moe_permute_noalloc: lives in the library image of every device that
+// loads it.  Head: status int[8] at 0, counts int[256] at 256, tile_prefix int[257] at 1536;
+// then pair_row int[B200MOE_NOALLOC_MAX_TOKENS * 8] at 4096.
+constexpr size_t NOALLOC_HEAD_BYTES = 4096;
+constexpr size_t NOALLOC_SCRATCH_BYTES = NOALLOC_HEAD_BYTES + (size_t)B200MOE_NOALLOC_MAX_TOKENS * 8 * 4;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+unsigned char* g_noalloc_dev_ptr[NOALLOC_MAX_DEVICES];   // device address of the array, per device (host copy)
+std::mutex g_noalloc_mutex;
+
 int check_ws(b200moe_ctx* h, int T, void* ws, size_t ws_bytes, b200moe_ws_layout* L) {
     layout(h->cfg, T, L);
     if (!ws || ws_bytes < L->total_bytes || (reinterpret_cast<uintptr_t>(ws) & 255)) return B200MOE_E_WORKSPACE;
@@ -419,6 +430,54 @@ int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const floa
                        false, ws, L, st);
 }
 
+int b200moe_permute_noalloc(b200moe_handle h, const int32_t* topk_idx, const float* topk_w, int T, int local_offset,
+                            int32_t* expert_row0, int32_t* row_token, float* row_w, int rows_capacity, void* stream) {
+    if (!h || T < 0) return B200MOE_E_BADARG;
+    if (T > B200MOE_NOALLOC_MAX_TOKENS) return B200MOE_E_TOO_LARGE;
+    if (!topk_idx || !topk_w || !expert_row0 || !row_token || !row_w) return B200MOE_E_BADARG;
+    const b200moe_config& c = h->cfg;
+    if (rows_capacity < rows_capacity_for(c, T)) return B200MOE_E_WORKSPACE;
+    int dev = -1;
+    CU_TRY(cudaGetDevice(&dev));
+    if (dev != h->device || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return B200MOE_E_BADARG;
+    unsigned char* scratch = nullptr;
+    {
+        // Once per device, with that device current: the array's name is only a host-side stand-in,
+        // the kernels need its device address.
+        std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+        if (!g_noalloc_dev_ptr[dev]) {
+            void* p = nullptr;
+            CU_TRY(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+            if (!p) return B200MOE_E_DRIVER;
+            g_noalloc_dev_ptr[dev] = static_cast<unsigned char*>(p);
+        }
+        scratch = g_noalloc_dev_ptr[dev];
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int El = c.num_local_experts;
+    // the histogram and the status words must start at zero; the array keeps the last call's contents
+    CU_TRY(cudaMemsetAsync(scratch, 0, NOALLOC_HEAD_BYTES, st));
+    if (T > 0) {
+        const int n = T * c.top_k;
+        int grid = (n + 255) / 256;
+        if (grid > h->num_sms * 4) grid = h->num_sms * 4;
+        count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, local_offset, El, reinterpret_cast<int*>(scratch + 256));
+        CU_TRY(cudaGetLastError());
+    }
+    PlanParams pp;
+    pp.T = T; pp.top_k = c.top_k; pp.num_local = El; pp.local_offset = local_offset;
+    pp.token_tile = pick_token_tile(c, T);
+    pp.topk_idx = topk_idx; pp.topk_w = topk_w;
+    pp.status = reinterpret_cast<int*>(scratch);
+    pp.counts = reinterpret_cast<int*>(scratch + 256);
+    pp.tile_prefix = reinterpret_cast<int*>(scratch + 1536);
+    pp.pair_row = reinterpret_cast<int32_t*>(scratch + NOALLOC_HEAD_BYTES);
+    pp.expert_row0 = expert_row0; pp.row_token = row_token; pp.row_w = row_w; pp.rows_cap = rows_capacity;
+    permute_kernel<<<El, 256, 0, st>>>(pp);
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
 int b200moe_status(b200moe_handle h, const void* workspace, void* stream, int* word) {
     if (!h || !workspace || !word) return B200MOE_E_BADARG;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -435,6 +494,7 @@ const char* b200moe_strerror(int code) {
         case B200MOE_E_DRIVER: return "cuTensorMapEncodeTiled unavailable or failed";
         case B200MOE_E_DEVICE: return "device is not compute capability 10.x";
         case B200MOE_E_KERNEL: return "a kernel gave up a bounded wait or met a bad schedule (see status word)";
+        case B200MOE_E_TOO_LARGE: return "num_tokens exceeds B200MOE_NOALLOC_MAX_TOKENS (the static scratch array is fixed-size)";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
     }
 }

@@ -163,6 +163,18 @@ class MoELayer:
             _lib.check(rc, "b200moe_route")
         return idx, w
 
+    def permute_noalloc(self, topk_idx, topk_w, local_expert_offset, expert_row0, row_token, row_w):
+        """Expert-sorted row map into caller-provided tensors through the entry point that keeps its
+        scratch in a static device array (for hosts that must not allocate device memory); at most
+        `_lib.NOALLOC_MAX_TOKENS` tokens, calls on one device must not overlap."""
+        T = int(topk_idx.shape[0])
+        stream = torch.cuda.current_stream(topk_idx.device).cuda_stream
+        rc = _lib.lib.b200moe_permute_noalloc(self._h, _ptr(_contig(topk_idx)), _ptr(_contig(topk_w)), T,
+                                              _scalar(local_expert_offset, int), _ptr(expert_row0),
+                                              _ptr(row_token), _ptr(row_w), int(row_token.numel()),
+                                              C.c_void_p(stream))
+        _lib.check(rc, "b200moe_permute_noalloc")
+
     def _check(self, logits, bias, hs, hss, w13, s13, w2, s2, T):
         s = self.shape
         H, I, E, El = s.hidden, s.intermediate, s.num_experts, s.num_local_experts
