@@ -68,6 +68,8 @@ typedef struct b200moe_ws_layout {
     size_t act_lo;        /* uint8[rows_cap, I] e4m3 of the rounding residual              */
     size_t act_scale;     /* float[I/128, rows_cap]                                        */
     size_t y;             /* float[rows_cap, H] weighted expert outputs per row            */
+    size_t sk_count;      /* int32[2][2*SMs] arrival counters of K-split units (GEMM1, GEMM2)*/
+    size_t sk_partial;    /* float[2*SMs][32768] fp32 partial accumulators of K-split units */
     size_t rows_cap;      /* number of rows the row-indexed buffers hold                   */
     size_t token_tile;    /* tokens per GEMM tile chosen for this T                        */
     size_t total_bytes;

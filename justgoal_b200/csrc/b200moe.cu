@@ -83,7 +83,8 @@ int rows_capacity_for(const b200moe_config& c, int T) {
     return (int)rows;
 }
 
-void layout(const b200moe_config& c, int T, b200moe_ws_layout* L) {
+void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
+    const b200moe_config& c = h->cfg;
     const size_t A = 256;
     const int El = c.num_local_experts, K = c.top_k;
     const size_t rows = (size_t)rows_capacity_for(c, T);
@@ -91,6 +92,7 @@ void layout(const b200moe_config& c, int T, b200moe_ws_layout* L) {
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, A); return o; };
     L->status = take(8 * 4);
     L->counts = take((size_t)El * 4);
+    L->sk_count = take((size_t)2 * 2 * h->num_sms * 4);       // [GEMM1 | GEMM2][2 * grid]; zeroed with the head
     L->expert_row0 = take((size_t)(El + 1) * 4);
     L->tile_prefix = take((size_t)(El + 1) * 4);
     L->topk_idx = take((size_t)T * K * 4);
@@ -104,6 +106,7 @@ void layout(const b200moe_config& c, int T, b200moe_ws_layout* L) {
     L->act_lo = take(rows * c.intermediate);
     L->act_scale = take((size_t)(c.intermediate / 128) * rows * 4);
     L->y = take(rows * c.hidden * 4);
+    L->sk_partial = take((size_t)2 * h->num_sms * SK_SLOT_FLOATS_MAX * 4);
     L->rows_cap = rows;
     L->token_tile = (size_t)pick_token_tile(c, T);
     L->total_bytes = off;
@@ -235,6 +238,8 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g1.w_scale = static_cast<const float*>(s13); g1.b_scale = a_scale; g1.rows_cap = rows_cap;
     g1.act_hi = act_hi; g1.act_lo = act_lo; g1.act_scale = act_scale; g1.I = I; g1.H = H;
     g1.evict_first_weights = ntok < 128;
+    g1.sk_count = reinterpret_cast<int*>(ws + L.sk_count);
+    g1.sk_partial = reinterpret_cast<float*>(ws + L.sk_partial);
     CU_TRY(launch_gemm_ntok<true>(ntok, h->num_sms, st, m_w13, m_a, m_a, g1));
     CU_TRY(prof_mark(h, 4, st));
 
@@ -245,6 +250,8 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g2.w_scale = static_cast<const float*>(s2); g2.b_scale = act_scale; g2.rows_cap = rows_cap;
     g2.row_w = row_w; g2.y = y; g2.H = H; g2.I = I;
     g2.evict_first_weights = ntok < 128;
+    g2.sk_count = reinterpret_cast<int*>(ws + L.sk_count) + 2 * h->num_sms;
+    g2.sk_partial = g1.sk_partial;
     CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
     CU_TRY(prof_mark(h, 5, st));
 
@@ -270,7 +277,7 @@ unsigned char* g_noalloc_dev_ptr[NOALLOC_MAX_DEVICES];   // device address of th
 std::mutex g_noalloc_mutex;
 
 int check_ws(b200moe_ctx* h, int T, void* ws, size_t ws_bytes, b200moe_ws_layout* L) {
-    layout(h->cfg, T, L);
+    layout(h, T, L);
     if (!ws || ws_bytes < L->total_bytes || (reinterpret_cast<uintptr_t>(ws) & 255)) return B200MOE_E_WORKSPACE;
     return 0;
 }
@@ -342,14 +349,14 @@ int b200moe_profile_read(b200moe_handle h, int slot, float* stage_ms) {
 
 int b200moe_workspace_layout(b200moe_handle h, int num_tokens, b200moe_ws_layout* L) {
     if (!h || !L || num_tokens < 0) return B200MOE_E_BADARG;
-    layout(h->cfg, num_tokens, L);
+    layout(h, num_tokens, L);
     return 0;
 }
 
 int b200moe_workspace_bytes(b200moe_handle h, int num_tokens, size_t* bytes) {
     if (!h || !bytes || num_tokens < 0) return B200MOE_E_BADARG;
     b200moe_ws_layout L;
-    layout(h->cfg, num_tokens, &L);
+    layout(h, num_tokens, &L);
     *bytes = L.total_bytes;
     return 0;
 }

@@ -7,7 +7,7 @@
 //               stored as TWO e4m3 values hi = rn(c/scale), lo = rn(c/scale - hi) under one scale.
 //   GEMM2 (G2): D[128, NTOK] = W2[e, mt*128 .. +128, :] . (act_hi + act_lo)[rows]^T, two MMAs per
 //               K step into the same accumulator; epilogue: y[row, h] = row_w[row] * D.
-// Block scales change every 128 K, so each 128-K block is accumulated into a fresh TMEM buffer
+// Block scales change every 128 K, so each 128-K block is accumulated into a fresh TMEM region
 // and promoted into fp32 registers: acc += part * (token_scale[kb] * weight_scale[kb]).
 // The same arithmetic is stated by the reference's tcgen05 kernels
 // (kda05_reproduction_full_shape/fable-5.1/moe_fp8_fwd/<def>/fable51_moe_v94/kernel.cu:3336,3441-3446
@@ -16,8 +16,17 @@
 // unlike them the SwiGLU output keeps a second e4m3 term, because a single e4m3 per element
 // does not meet an absolute/relative tolerance of 1e-2 against the unquantised definition.
 //
+// Schedule: K is cut into GROUPS of KPB 128-K blocks (one TMEM hand-off per group).  The
+// kernel is persistent; the flat list of (unit, group) pairs is cut into gridDim.x equal
+// contiguous ranges ("stream-K"), so every SM streams weights for the whole kernel.  A unit
+// whose groups fall into several CTAs is finished by whichever of them arrives last: each
+// writes its fp32 partial to its own slot, bumps a counter, and the last one adds the slots in
+// CTA order (a fixed order: results are bit-identical from run to run) and runs the epilogue.
+// Nobody waits for another CTA.
+//
 // Warp roles: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) + TMEM owner,
-// warps 2.. = promotion/epilogue (4 or 8 warps; warp % 4 selects the TMEM lane quarter).
+// warps 2-3 idle (they complete the first warpgroup so register re-allocation is legal),
+// warps 4.. = promotion/epilogue (4 or 8 warps; warp % 4 selects the TMEM lane quarter).
 // Every wait is bounded (common.cuh); no TMA load uses cluster multicast.
 #pragma once
 #include <cuda_fp16.h>
@@ -43,6 +52,8 @@ struct GemmParams {
     uint8_t* act_hi; uint8_t* act_lo; float* act_scale; int I;   // GEMM1 outputs
     const float* row_w; float* y; int H;                          // GEMM2 outputs
     int evict_first_weights;
+    int* sk_count;        // [2 * gridDim.x] arrival counters of split units (zero at launch)
+    float* sk_partial;    // [2 * gridDim.x] slots of SLOT_FLOATS floats
 };
 
 template <int NTOK, bool G1>
@@ -54,23 +65,37 @@ struct GemmCfg {
     static constexpr int SC_OFF = NA * A_BYTES + NB * B_BYTES;
     static constexpr int STAGE_BYTES = SC_OFF + 1024;
     static constexpr int TX_BYTES = NA * A_BYTES + NB * B_BYTES + NTOK * 4;
-    static constexpr int STAGES_RAW = (212 * 1024) / STAGE_BYTES;
+    static constexpr int STAGES_RAW = (208 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int CPB = (G1 ? 2 : 1) * NTOK;        // TMEM columns per accumulator buffer
-    static constexpr int NACC = (512 / CPB) > 4 ? 4 : (512 / CPB);
-    static constexpr int TMEM_COLS = NACC * CPB;
-    static constexpr int NPW = CPB > 128 ? 8 : 4;          // promotion warps
-    static constexpr int NC = NTOK / (NPW / 4);            // token columns per promotion thread
     static constexpr int NACCUM = G1 ? 2 : 1;
-    static constexpr int NTHREADS = 64 + 32 * NPW;
+    // Dependent MMAs into one accumulator serialise on the tensor pipe's latency, which dominates
+    // for narrow token tiles; the MMAs of one K block are therefore spread over NSPLIT independent
+    // partial accumulators (GEMM1: even/odd K step; GEMM2: hi/lo x even/odd) that the promotion adds.
+    static constexpr int NSPLIT = G1 ? (NTOK <= 32 ? 2 : 1) : (NTOK <= 32 ? 4 : (NTOK == 64 ? 2 : 1));
+    static constexpr int CPB = NACCUM * NSPLIT * NTOK;     // TMEM columns per K block
+    static constexpr int KPB = (128 / CPB) < 1 ? 1 : (128 / CPB);
+    static constexpr int BUFCOLS = KPB * CPB;               // TMEM columns per hand-off buffer
+    static constexpr int NACC = (512 / BUFCOLS) > 4 ? 4 : (512 / BUFCOLS);
+    static constexpr int TMEM_COLS = NACC * BUFCOLS;
+    static constexpr int NPW = NTOK >= 64 ? 8 : 4;         // promotion warps
+    static constexpr int NPT = 32 * NPW;                   // promotion threads
+    static constexpr int NC = NTOK / (NPW / 4);            // token columns per promotion thread
+    static constexpr int CH = (NACCUM * NC > 64) ? 16 : (NC < 32 ? NC : 32);   // columns per tcgen05.ld
+    static constexpr int NTHREADS = 128 + NPT;
+    static constexpr bool REALLOC_REGS = NPW == 8;
+    static constexpr int SLOT_FLOATS = NACCUM * NC * NPT;  // = NACCUM * 128 * NTOK
     static constexpr int TABLE_INTS = 3 * (MAX_LOCAL + 1);
     static constexpr int RED_BYTES = NPW * NC * 4;
     static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * STAGE_BYTES + 256 /*barriers*/ +
-                                      TABLE_INTS * 4 + RED_BYTES;
+                                      TABLE_INTS * 4 + RED_BYTES + 16;
     static_assert(NTOK % 16 == 0 && NTOK >= 16 && NTOK <= 128, "token tile");
     static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "tmem");
+    static_assert(STAGES >= KPB + 1, "a group must fit the stage ring with room to prefetch");
+    static_assert(NC % CH == 0 && (CH == 16 || CH == 32), "chunking");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
+
+constexpr int SK_SLOT_FLOATS_MAX = 2 * 128 * 128;   // largest SLOT_FLOATS (GEMM1, 128 tokens)
 
 struct Unit { int e, mt, tt, row0, nvalid; };
 
@@ -94,7 +119,41 @@ __device__ __forceinline__ bool decode_unit(int u, int n_mtiles, int num_local, 
     return o.mt < n_mtiles && o.nvalid > 0;
 }
 
+// First flat (unit, group) index of CTA c, and the CTA that owns flat index x.
+__device__ __forceinline__ long long sk_start(long long c, long long total, long long grid) { return c * total / grid; }
+__device__ __forceinline__ int sk_owner(long long x, long long total, long long grid) {
+    long long c = x * grid / total;
+    while (c + 1 < grid && sk_start(c + 1, total, grid) <= x) ++c;
+    while (c > 0 && sk_start(c, total, grid) > x) --c;
+    return (int)c;
+}
+
 __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, float* v) {
+    uint32_t r[N];
+    if constexpr (N == 16) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(taddr) : "memory");
+    } else {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr) : "memory");
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) v[i] = __uint_as_float(r[i]);
+}
 
 template <int NTOK, bool G1>
 __global__ void __launch_bounds__(GemmCfg<NTOK, G1>::NTHREADS, 1)
@@ -104,19 +163,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tail = smem + C::STAGES * C::STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tail);             // full[S], empty[S], tfull[NACC], tempty[NACC], red[2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail);     // full[S], empty[S], tfull[NACC], tempty[NACC], red[2]
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tail + 240);
     int* s_tiles = reinterpret_cast<int*>(tail + 256);
     int* s_row0 = s_tiles + (MAX_LOCAL + 1);
     int* s_cnt = s_row0 + (MAX_LOCAL + 1);
     uint32_t* s_red = reinterpret_cast<uint32_t*>(s_cnt + (MAX_LOCAL + 1));
+    int* s_flag = reinterpret_cast<int*>(s_red + C::NPW * C::NC);   // [2] arrival order of a split unit, per group
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t bar_full = smem_u32(bars);
     const uint32_t bar_empty = bar_full + 8 * C::STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * C::STAGES;
     const uint32_t bar_tempty = bar_tfull + 8 * C::NACC;
-    const uint32_t bar_red = bar_tempty + 8 * C::NACC;    // one per column group: 4 warps meet here (bounded)
+    const uint32_t bar_red = bar_tempty + 8 * C::NACC;    // one per column group: its 4 warps meet here (bounded)
     static_assert(8 * (2 * C::STAGES + 2 * C::NACC + 2) <= 240, "barrier area");
 
     if (threadIdx.x == 0) {
@@ -137,22 +197,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
-    const int total_units = s_tiles[p.num_local] * p.n_mtiles;
     const uint32_t smem_base = smem_u32(smem);
 
+    // flat schedule: (unit, group) pairs, this CTA's contiguous share
+    const int NG = (p.KB + C::KPB - 1) / C::KPB;
+    const long long total = (long long)s_tiles[p.num_local] * p.n_mtiles * NG;
+    // with fewer pairs than CTAs only the first `total` CTAs take part, so that every
+    // participating CTA owns at least one pair (the split-unit bookkeeping counts on that)
+    const long long grid = total < (long long)gridDim.x ? (total > 0 ? total : 1) : (long long)gridDim.x;
+    const bool has_work = (long long)blockIdx.x < grid && total > 0;
+    const long long g_lo = has_work ? sk_start(blockIdx.x, total, grid) : 0;
+    const long long g_hi = has_work ? sk_start(blockIdx.x + 1, total, grid) : 0;
+
+    if (warp < 4) {
+    // ================================================================ control warpgroup
+    if (C::REALLOC_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             const uint64_t pol = policy_evict_first();
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+            for (long long g = g_lo; g < g_hi && ok;) {
+                const int u = (int)(g / NG), gb = (int)(g - (long long)u * NG);
+                const int ge = (int)min((long long)NG, gb + (g_hi - g));
+                g += ge - gb;
                 Unit un;
                 if (!decode_unit(u, p.n_mtiles, p.num_local, NTOK, s_tiles, s_row0, s_cnt, un)) {
                     atomicCAS(p.status, 0, ERR_BAD_SCHEDULE); break;
                 }
                 const int wrow = un.e * p.rows_per_expert + un.mt * 128;
-                for (int kb = 0; kb < p.KB; ++kb) {
+                const int kb_end = min(p.KB, ge * C::KPB);
+                for (int kb = gb * C::KPB; kb < kb_end; ++kb) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, p.status, ERR_WAIT_SMEM_EMPTY)) { ok = false; break; }
                     const uint32_t st = smem_base + stage * C::STAGE_BYTES;
                     const uint32_t full = bar_full + 8 * stage;
@@ -183,53 +259,89 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             int stage = 0; uint32_t phase = 0;
             int ab = 0; uint32_t aphase = 0;
             bool ok = true;
-            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-                for (int kb = 0; kb < p.KB; ++kb) {
-                    if (!mbar_wait(bar_full + 8 * stage, phase, p.status, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
+            for (long long g = g_lo; g < g_hi && ok;) {
+                const int u = (int)(g / NG), gb = (int)(g - (long long)u * NG);
+                const int ge = (int)min((long long)NG, gb + (g_hi - g));
+                g += ge - gb;
+                for (int grp = gb; grp < ge && ok; ++grp) {
                     if (!mbar_wait(bar_tempty + 8 * ab, aphase ^ 1, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t st = smem_base + stage * C::STAGE_BYTES;
-                    const uint32_t d = tmem_base + ab * C::CPB;
-                    if (G1) {
-                        const uint64_t a_up = make_smem_desc(st);
-                        const uint64_t a_gate = make_smem_desc(st + C::A_BYTES);
-                        const uint64_t b = make_smem_desc(st + 2 * C::A_BYTES);
+                    const int nj = min(C::KPB, p.KB - grp * C::KPB);
+                    for (int j = 0; j < nj; ++j) {
+                        if (!mbar_wait(bar_full + 8 * stage, phase, p.status, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t st = smem_base + stage * C::STAGE_BYTES;
+                        const uint32_t d = tmem_base + ab * C::BUFCOLS + j * C::CPB;
+                        if (G1) {
+                            const uint64_t a_up = make_smem_desc(st);
+                            const uint64_t a_gate = make_smem_desc(st + C::A_BYTES);
+                            const uint64_t b = make_smem_desc(st + 2 * C::A_BYTES);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            umma_f8(d, a_up + 2 * k, b + 2 * k, idesc, k > 0);
-                            umma_f8(d + NTOK, a_gate + 2 * k, b + 2 * k, idesc, k > 0);
+                            for (int k = 0; k < 4; ++k) {
+                                const int sp = k % C::NSPLIT;
+                                umma_f8(d + sp * NTOK, a_up + 2 * k, b + 2 * k, idesc, k >= C::NSPLIT);
+                                umma_f8(d + (C::NSPLIT + sp) * NTOK, a_gate + 2 * k, b + 2 * k, idesc, k >= C::NSPLIT);
+                            }
+                        } else {
+                            const uint64_t a = make_smem_desc(st);
+                            const uint64_t bh = make_smem_desc(st + C::A_BYTES);
+                            const uint64_t bl = make_smem_desc(st + C::A_BYTES + C::B_BYTES);
+                            if (C::NSPLIT == 1) {
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) umma_f8(d, a + 2 * k, bh + 2 * k, idesc, k > 0);
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) umma_f8(d, a + 2 * k, bl + 2 * k, idesc, 1);
+                            } else {
+                                constexpr int HS = C::NSPLIT / 2;      // partial accumulators per operand half
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) {
+                                    const int sp = k % HS;
+                                    umma_f8(d + sp * NTOK, a + 2 * k, bh + 2 * k, idesc, k >= HS);
+                                    umma_f8(d + (HS + sp) * NTOK, a + 2 * k, bl + 2 * k, idesc, k >= HS);
+                                }
+                            }
                         }
-                    } else {
-                        const uint64_t a = make_smem_desc(st);
-                        const uint64_t bh = make_smem_desc(st + C::A_BYTES);
-                        const uint64_t bl = make_smem_desc(st + C::A_BYTES + C::B_BYTES);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) umma_f8(d, a + 2 * k, bh + 2 * k, idesc, k > 0);
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) umma_f8(d, a + 2 * k, bl + 2 * k, idesc, 1);
+                        umma_commit(bar_empty + 8 * stage);
+                        if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                     }
-                    umma_commit(bar_empty + 8 * stage);
+                    if (!ok) break;
                     umma_commit(bar_tfull + 8 * ab);
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                     if (++ab == C::NACC) { ab = 0; aphase ^= 1; }
                 }
             }
         }
         __syncwarp();
+    }
     } else {
         // ------------------------------------------------------------ promotion + epilogue
-        const int pw = warp - 2;
+        if (C::REALLOC_REGS) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        const int pw = warp - 4;
         const int quarter = warp & 3;                  // TMEM lanes [32*quarter, +32)
-        const int grp = pw >> 2;                       // column group (0 when NPW == 4)
-        const int c0 = grp * C::NC;
+        const int grp_id = pw >> 2;                    // column group (0 when NPW == 4)
+        const int c0 = grp_id * C::NC;
         const int m = quarter * 32 + lane;             // weight row inside the tile
+        const int ptid = threadIdx.x - 128;
         const uint32_t tlane = (uint32_t)(quarter * 32) << 16;
+        const uint32_t my_red = bar_red + 8 * grp_id;
         int stage = 0; uint32_t phase = 0;
         int ab = 0; uint32_t aphase = 0;
         uint32_t rphase = 0;
         bool ok = true;
         float acc[C::NACCUM][C::NC];
-        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+
+        // the 4 warps of one column group meet (bounded); false = gave up
+        auto group_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(my_red);
+            const bool r = mbar_wait(my_red, rphase, p.status, ERR_WAIT_GROUP);
+            rphase ^= 1;
+            return r;
+        };
+
+        for (long long g = g_lo; g < g_hi && ok;) {
+            const int u = (int)(g / NG), gb = (int)(g - (long long)u * NG);
+            const int ge = (int)min((long long)NG, gb + (g_hi - g));
+            const bool first_seg = (g == g_lo);
+            g += ge - gb;
             Unit un;
             if (!decode_unit(u, p.n_mtiles, p.num_local, NTOK, s_tiles, s_row0, s_cnt, un)) break;
 #pragma unroll
@@ -238,39 +350,114 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 for (int i = 0; i < C::NC; ++i) acc[a][i] = 0.f;
             const float* ws0 = p.w_scale + ((size_t)un.e * p.scale_rows + un.mt) * p.KB;
             const float* ws1 = G1 ? ws0 + (size_t)(p.gate_offset >> 7) * p.KB : ws0;
-            float sw0n = __ldg(ws0), sw1n = G1 ? __ldg(ws1) : 0.f;
-            for (int kb = 0; kb < p.KB; ++kb) {
-                const float sw0 = sw0n, sw1 = sw1n;
-                if (kb + 1 < p.KB) { sw0n = __ldg(ws0 + kb + 1); if (G1) sw1n = __ldg(ws1 + kb + 1); }
+
+            for (int grp = gb; grp < ge; ++grp) {
+                const int kb0 = grp * C::KPB;
+                const int nj = min(C::KPB, p.KB - kb0);
+                float sw[C::KPB][C::NACCUM];
+#pragma unroll
+                for (int j = 0; j < C::KPB; ++j) {
+                    const int kb = min(kb0 + j, p.KB - 1);
+                    sw[j][0] = __ldg(ws0 + kb);
+                    if (G1) sw[j][1] = __ldg(ws1 + kb);
+                }
                 if (!mbar_wait(bar_tfull + 8 * ab, aphase, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
-                // the token scales of this stage arrived with the same transaction barrier as the tiles
-                if (!mbar_wait(bar_full + 8 * stage, phase, p.status, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
                 tc_fence_after();
-                const float* sc = reinterpret_cast<const float*>(smem + stage * C::STAGE_BYTES + C::SC_OFF) + c0;
-                const uint32_t tcol = tmem_base + tlane + ab * C::CPB + c0;
+                const uint32_t tbuf = tmem_base + tlane + ab * C::BUFCOLS + c0;
+
+                // flattened chunk list (j, column chunk, accumulator); the tcgen05.ld of chunk k+1 is in
+                // flight while chunk k is folded into the accumulators
+                constexpr int NCH = C::NC / C::CH;
+                constexpr int NK = C::KPB * NCH * C::NACCUM * C::NSPLIT;
+                float part[2][C::CH];
+                tmem_ld_chunk<C::CH>(tbuf, part[0]);
+                const int st0 = stage;
 #pragma unroll
-                for (int ch = 0; ch < C::NC / 16; ++ch) {
-                    float4 s4[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) s4[j] = *reinterpret_cast<const float4*>(sc + ch * 16 + j * 4);
-                    const float* sv = reinterpret_cast<const float*>(s4);
-#pragma unroll
-                    for (int a = 0; a < C::NACCUM; ++a) {
-                        float part[16];
-                        tmem_ld16(tcol + a * NTOK + ch * 16, part);
+                for (int k = 0; k < NK; ++k) {
+                    const int sp = k % C::NSPLIT;
+                    const int a = (k / C::NSPLIT) % C::NACCUM;
+                    const int ch = (k / (C::NSPLIT * C::NACCUM)) % NCH;
+                    const int j = k / (C::NSPLIT * C::NACCUM * NCH);
+                    if (j < nj) {
                         tmem_wait_ld();
-                        const float sw = a == 0 ? sw0 : sw1;
+                        if (k + 1 < NK) {
+                            const int sp1 = (k + 1) % C::NSPLIT;
+                            const int a1 = ((k + 1) / C::NSPLIT) % C::NACCUM;
+                            const int ch1 = ((k + 1) / (C::NSPLIT * C::NACCUM)) % NCH;
+                            const int j1 = (k + 1) / (C::NSPLIT * C::NACCUM * NCH);
+                            if (j1 < nj)
+                                tmem_ld_chunk<C::CH>(tbuf + j1 * C::CPB + (a1 * C::NSPLIT + sp1) * NTOK + ch1 * C::CH,
+                                                     part[(k + 1) & 1]);
+                        }
+                        int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
+                        if (ch == 0 && a == 0 && sp == 0) {
+                            // token scales of this K block arrived with the stage's transaction barrier
+                            const uint32_t ph = (st0 + j >= C::STAGES) ? (phase ^ 1) : phase;
+                            if (!mbar_wait(bar_full + 8 * sj, ph, p.status, ERR_WAIT_SMEM_FULL)) ok = false;
+                        }
+                        const float* sc = reinterpret_cast<const float*>(smem + sj * C::STAGE_BYTES + C::SC_OFF) + c0 + ch * C::CH;
+                        const float swa = sw[j][a];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) acc[a][ch * 16 + i] = fmaf(part[i], sv[i] * sw, acc[a][ch * 16 + i]);
+                        for (int i = 0; i < C::CH; i += 4) {
+                            const float4 s4 = *reinterpret_cast<const float4*>(sc + i);
+                            const float2 m0 = __fmul2_rn(make_float2(s4.x, s4.y), make_float2(swa, swa));
+                            const float2 m1 = __fmul2_rn(make_float2(s4.z, s4.w), make_float2(swa, swa));
+                            float* ac = &acc[a][ch * C::CH + i];
+                            const float2 r0 = __ffma2_rn(make_float2(part[k & 1][i], part[k & 1][i + 1]), m0, make_float2(ac[0], ac[1]));
+                            const float2 r1 = __ffma2_rn(make_float2(part[k & 1][i + 2], part[k & 1][i + 3]), m1, make_float2(ac[2], ac[3]));
+                            ac[0] = r0.x; ac[1] = r0.y; ac[2] = r1.x; ac[3] = r1.y;
+                        }
                     }
                 }
+                if (!ok) break;
+                // all tcgen05.ld of this buffer have completed (the last wait above) and all scale reads are done
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) { mbar_arrive(bar_tempty + 8 * ab); mbar_arrive(bar_empty + 8 * stage); }
-                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                if (lane == 0) {
+                    mbar_arrive(bar_tempty + 8 * ab);
+                    for (int j = 0; j < nj; ++j) {
+                        int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
+                        mbar_arrive(bar_empty + 8 * sj);
+                    }
+                }
+                stage += nj;
+                if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
                 if (++ab == C::NACC) { ab = 0; aphase ^= 1; }
             }
             if (!ok) break;
+
+            if (!(gb == 0 && ge == NG)) {
+                // ---- split unit: publish the partial, the last CTA to arrive adds them up in CTA order
+                const long long u0 = (long long)u * NG;
+                const int c_first = sk_owner(u0, total, grid), c_last = sk_owner(u0 + NG - 1, total, grid);
+                float* slot = p.sk_partial + (size_t)(blockIdx.x * 2 + (first_seg ? 0 : 1)) * SK_SLOT_FLOATS_MAX;
+#pragma unroll
+                for (int a = 0; a < C::NACCUM; ++a)
+#pragma unroll
+                    for (int i = 0; i < C::NC; ++i) __stcg(slot + (size_t)(a * C::NC + i) * C::NPT + ptid, acc[a][i]);
+                __threadfence();
+                if (!group_sync()) { ok = false; break; }
+                if (quarter == 0 && lane == 0) {
+                    s_flag[grp_id] = atomicAdd(p.sk_count + c_first * 2 + grp_id, 1);
+                }
+                if (!group_sync()) { ok = false; break; }
+                const bool last = s_flag[grp_id] == (c_last - c_first);
+                if (!group_sync()) { ok = false; break; }          // s_flag may be rewritten by the next split unit
+                if (!last) continue;
+                __threadfence();
+#pragma unroll
+                for (int a = 0; a < C::NACCUM; ++a)
+#pragma unroll
+                    for (int i = 0; i < C::NC; ++i) acc[a][i] = 0.f;
+                for (int c = c_first; c <= c_last; ++c) {
+                    const bool c_first_seg = (int)(sk_start(c, total, grid) / NG) == u;
+                    const float* src = p.sk_partial + (size_t)(c * 2 + (c_first_seg ? 0 : 1)) * SK_SLOT_FLOATS_MAX;
+#pragma unroll
+                    for (int a = 0; a < C::NACCUM; ++a)
+#pragma unroll
+                        for (int i = 0; i < C::NC; ++i) acc[a][i] += __ldcg(src + (size_t)(a * C::NC + i) * C::NPT + ptid);
+                }
+            }
 
             if (G1) {
                 // SwiGLU, then amax over the 128 rows of the tile for every token column
@@ -282,11 +469,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     const uint32_t wm = __reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(v)));
                     if (lane == 0) red[i] = wm;
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_red + 8 * grp);
-                if (!mbar_wait(bar_red + 8 * grp, rphase, p.status, ERR_WAIT_GROUP)) { ok = false; break; }
-                rphase ^= 1;
-                const uint32_t* rg = s_red + grp * 4 * C::NC;
+                if (!group_sync()) { ok = false; break; }
+                const uint32_t* rg = s_red + grp_id * 4 * C::NC;
                 const size_t col = (size_t)un.mt * 128 + m;
 #pragma unroll
                 for (int i = 0; i < C::NC; i += 2) {
@@ -314,10 +498,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         }
                     }
                 }
-                __syncwarp();                                   // s_red is reused by the next unit
-                if (lane == 0) mbar_arrive(bar_red + 8 * grp);
-                if (!mbar_wait(bar_red + 8 * grp, rphase, p.status, ERR_WAIT_GROUP)) { ok = false; break; }
-                rphase ^= 1;
+                if (!group_sync()) { ok = false; break; }          // s_red is reused by the next unit
             } else {
                 const size_t col = (size_t)un.mt * 128 + m;
 #pragma unroll

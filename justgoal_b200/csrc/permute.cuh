@@ -51,19 +51,43 @@ __global__ void __launch_bounds__(256) permute_kernel(const PlanParams p) {
     __shared__ int s_scan[256];
     const int e = blockIdx.x, tid = threadIdx.x;
 
-    if (tid == 0) {
+    if (tid < 32) {
+        // warp-parallel exclusive scan over the (<= 256) counts: lane l owns experts [l*per, (l+1)*per)
+        const int per = (p.num_local + 31) / 32;
+        int c[MAX_LOCAL / 32];
         int rows = 0, tiles = 0, pairs = 0, active = 0;
-        for (int i = 0; i < p.num_local; ++i) {
-            const int c = p.counts[i];
-            s_row0[i] = rows; s_tiles[i] = tiles;
-            rows += (c + ROW_ALIGN - 1) / ROW_ALIGN * ROW_ALIGN;
-            tiles += (c + p.token_tile - 1) / p.token_tile;
-            pairs += c; active += c > 0;
+#pragma unroll
+        for (int k = 0; k < MAX_LOCAL / 32; ++k) {
+            const int i = tid * per + k;
+            c[k] = (k < per && i < p.num_local) ? p.counts[i] : 0;
+            rows += (c[k] + ROW_ALIGN - 1) / ROW_ALIGN * ROW_ALIGN;
+            tiles += (c[k] + p.token_tile - 1) / p.token_tile;
+            pairs += c[k]; active += c[k] > 0;
         }
-        s_row0[p.num_local] = rows; s_tiles[p.num_local] = tiles;
-        if (e == 0) {
-            p.status[ST_PAIRS] = pairs; p.status[ST_ROWS] = rows;
-            p.status[ST_TILES] = tiles; p.status[ST_ACTIVE] = active;
+        int rows_in = rows, tiles_in = tiles;
+        for (int off = 1; off < 32; off <<= 1) {
+            const int r = __shfl_up_sync(0xFFFFFFFFu, rows_in, off);
+            const int t = __shfl_up_sync(0xFFFFFFFFu, tiles_in, off);
+            if (tid >= off) { rows_in += r; tiles_in += t; }
+        }
+        for (int off = 16; off; off >>= 1) {
+            pairs += __shfl_xor_sync(0xFFFFFFFFu, pairs, off);
+            active += __shfl_xor_sync(0xFFFFFFFFu, active, off);
+        }
+        int r0 = rows_in - rows, t0 = tiles_in - tiles;       // exclusive prefixes of this lane
+#pragma unroll
+        for (int k = 0; k < MAX_LOCAL / 32; ++k) {
+            const int i = tid * per + k;
+            if (k < per && i < p.num_local) {
+                s_row0[i] = r0; s_tiles[i] = t0;
+                r0 += (c[k] + ROW_ALIGN - 1) / ROW_ALIGN * ROW_ALIGN;
+                t0 += (c[k] + p.token_tile - 1) / p.token_tile;
+            }
+        }
+        if (tid == 31) { s_row0[p.num_local] = rows_in; s_tiles[p.num_local] = tiles_in; }
+        if (e == 0 && tid == 31) {
+            p.status[ST_PAIRS] = pairs; p.status[ST_ROWS] = rows_in;
+            p.status[ST_TILES] = tiles_in; p.status[ST_ACTIVE] = active;
         }
     }
     __syncthreads();
@@ -144,18 +168,22 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
     __shared__ int s_n;
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
         __syncthreads();
-        if (threadIdx.x == 0) {
-            int n = 0;
-            for (int k = 0; k < top_k; ++k) {
-                const int le = topk_idx[(size_t)t * top_k + k] - local_offset;
-                if (le >= 0 && le < num_local) {
-                    const int r = pair_row[(size_t)t * top_k + k];
-                    int j = n++;
-                    while (j > 0 && s_rows[j - 1] > r) { s_rows[j] = s_rows[j - 1]; --j; }
-                    s_rows[j] = r;
-                }
+        if (threadIdx.x < 32) {
+            // lanes 0..top_k-1 fetch their pair in parallel; rows are ranked by row index (= expert order)
+            const int lane = threadIdx.x;
+            int r = 0x7FFFFFFF;
+            if (lane < top_k) {
+                const int le = topk_idx[(size_t)t * top_k + lane] - local_offset;
+                if (le >= 0 && le < num_local) r = pair_row[(size_t)t * top_k + lane];
             }
-            s_n = n;
+            int rank = 0;
+            for (int j = 0; j < 8; ++j) {
+                const int rj = __shfl_sync(0xFFFFFFFFu, r, j);
+                rank += (rj < r) || (rj == r && j < lane);
+            }
+            const unsigned have = __ballot_sync(0xFFFFFFFFu, r != 0x7FFFFFFF);
+            if (r != 0x7FFFFFFF) s_rows[rank] = r;
+            if (lane == 0) s_n = __popc(have);
         }
         __syncthreads();
         const int n = s_n;

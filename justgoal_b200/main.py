@@ -50,7 +50,7 @@ class MoELayer:
 
     def __del__(self):
         h = getattr(self, "_h", None)
-        if h:
+        if h and _lib is not None and getattr(_lib, "lib", None) is not None:   # may run at interpreter exit
             _lib.lib.b200moe_destroy(h)
             self._h = None
 

@@ -69,22 +69,35 @@ def test_scaling_factor_doubling_is_exact(ds_weights):
     assert torch.equal((a.float() * 2).to(torch.bfloat16).view(torch.int16), b.view(torch.int16))
 
 
-def test_token_permutation_equivariance(ds_weights):
-    """Permuting the tokens permutes the output rows bit for bit (columns of a tile do not
-    interact; the combine order is by expert, not by arrival)."""
-    from justgoal_b200 import MoELayer
-    T = 1000
-    d = _inputs(T, ds_weights, 3)
-    layer = MoELayer(I.DEEPSEEK_V3)
-    a = layer.forward(*util.op_args(d)).clone()
-    perm = torch.randperm(T, generator=torch.Generator().manual_seed(1)).cuda()
+def _permuted(d, perm):
     d2 = dict(d)
     d2["routing_logits"] = d["routing_logits"][perm].contiguous()
     d2["hidden_states"] = d["hidden_states"].view(torch.uint8)[perm].contiguous().view(torch.float8_e4m3fn)
     d2["hidden_states_scale"] = d["hidden_states_scale"][:, perm].contiguous()
-    b = layer.forward(*util.op_args(d2))
-    torch.cuda.synchronize()
-    assert torch.equal(a[perm].view(torch.int16), b.view(torch.int16))
+    return d2
+
+
+def test_token_permutation_equivariance(ds_weights):
+    """Permuting the tokens permutes the output rows.  With one token tile per expert (T=64) the
+    result is bit-identical: columns of a tile do not interact and the combine order is by
+    expert.  With several tiles per expert a token may move to another tile, whose K range is
+    cut differently by the stream-K schedule (another fp32 summation order), so there only
+    the last bf16 bit of a few elements may move."""
+    from justgoal_b200 import MoELayer
+    layer = MoELayer(I.DEEPSEEK_V3)
+    for T, exact in ((64, True), (1000, False)):
+        d = _inputs(T, ds_weights, 3)
+        a = layer.forward(*util.op_args(d)).clone()
+        perm = torch.randperm(T, generator=torch.Generator().manual_seed(1)).cuda()
+        b = layer.forward(*util.op_args(_permuted(d, perm)))
+        torch.cuda.synchronize()
+        if exact:
+            assert torch.equal(a[perm].view(torch.int16), b.view(torch.int16))
+        else:
+            differs = (a[perm].view(torch.int16) != b.view(torch.int16)).float().mean().item()
+            assert differs < 2e-3, differs
+            rep = O.compare_output(b, a[perm], 1e-3, 8e-3)      # one bf16 ulp = 2^-8 relative
+            assert rep["fail_frac"] == 0.0, rep
 
 
 def test_nonzero_expert_offset_matches_shifted_weights(ds_weights):
