@@ -9,6 +9,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -30,6 +31,7 @@ struct b200moe_ctx {
     int prof_slots;            // 0 = profiling off
     long long prof_calls;      // forwards recorded since profiling was enabled
     cudaEvent_t* prof_events;  // [prof_slots][PROF_POINTS]
+    int ablate;                // B200MOE_ABLATE environment variable at create (timing experiments; 0 in normal use)
 };
 
 namespace {
@@ -58,8 +60,14 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
     cuuint64_t strides[1] = {cols};
     cuuint32_t box[2] = {128, box_rows};
     cuuint32_t estr[2] = {1, 1};
+    static int promo = -1;
+    if (promo < 0) { const char* e = getenv("B200MOE_L2PROMO"); promo = e ? atoi(e) : 3; }
+    const CUtensorMapL2promotion pm = promo == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                                    : promo == 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                    : promo == 2 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                 : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
     CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, pm,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : B200MOE_E_DRIVER;
 }
@@ -237,9 +245,12 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g1.KB = H / 128; g1.n_mtiles = I / 128; g1.rows_per_expert = 2 * I; g1.gate_offset = I; g1.scale_rows = 2 * I / 128;
     g1.w_scale = static_cast<const float*>(s13); g1.b_scale = a_scale; g1.rows_cap = rows_cap;
     g1.act_hi = act_hi; g1.act_lo = act_lo; g1.act_scale = act_scale; g1.I = I; g1.H = H;
-    g1.evict_first_weights = ntok < 128;
+    static int evf = -1;
+    if (evf < 0) { const char* e = getenv("B200MOE_EVICT_FIRST"); evf = e ? atoi(e) : 1; }
+    g1.evict_first_weights = evf && ntok < 128;
     g1.sk_count = reinterpret_cast<int*>(ws + L.sk_count);
     g1.sk_partial = reinterpret_cast<float*>(ws + L.sk_partial);
+    g1.ablate = h->ablate & 0xFF;
     CU_TRY(launch_gemm_ntok<true>(ntok, h->num_sms, st, m_w13, m_a, m_a, g1));
     CU_TRY(prof_mark(h, 4, st));
 
@@ -249,9 +260,10 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g2.KB = I / 128; g2.n_mtiles = H / 128; g2.rows_per_expert = H; g2.gate_offset = 0; g2.scale_rows = H / 128;
     g2.w_scale = static_cast<const float*>(s2); g2.b_scale = act_scale; g2.rows_cap = rows_cap;
     g2.row_w = row_w; g2.y = y; g2.H = H; g2.I = I;
-    g2.evict_first_weights = ntok < 128;
+    g2.evict_first_weights = evf && ntok < 128;
     g2.sk_count = reinterpret_cast<int*>(ws + L.sk_count) + 2 * h->num_sms;
     g2.sk_partial = g1.sk_partial;
+    g2.ablate = (h->ablate >> 8) & 0xFF;
     CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
     CU_TRY(prof_mark(h, 5, st));
 
@@ -311,6 +323,8 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     if (!h) return B200MOE_E_BADARG;
     h->cfg = *cfg; h->device = dev; h->num_sms = sms;
     h->prof_slots = 0; h->prof_calls = 0; h->prof_events = nullptr;
+    const char* ab = getenv("B200MOE_ABLATE");
+    h->ablate = ab ? atoi(ab) : 0;
     *out = h;
     return 0;
 }

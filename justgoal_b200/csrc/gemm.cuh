@@ -54,6 +54,8 @@ struct GemmParams {
     int evict_first_weights;
     int* sk_count;        // [2 * gridDim.x] arrival counters of split units (zero at launch)
     float* sk_partial;    // [2 * gridDim.x] slots of SLOT_FLOATS floats
+    int ablate;           // timing experiments only (results are wrong when non-zero): 1 = issue no MMA,
+                          // 2 = promotion skips tcgen05.ld/FMA, 4 = producer skips the token-side loads
 };
 
 template <int NTOK, bool G1>
@@ -83,6 +85,9 @@ struct GemmCfg {
     static constexpr int CH = (NACCUM * NC > 64) ? 16 : (NC < 32 ? NC : 32);   // columns per tcgen05.ld
     static constexpr int NTHREADS = 128 + NPT;
     static constexpr bool REALLOC_REGS = NPW == 8;
+    // narrow tiles: the promotion warps copy a group's token scales into registers as soon as the
+    // stage has landed and release the stage at once, instead of holding it until the group is folded
+    static constexpr bool EARLY_SCALES = KPB * NC <= 32;
     static constexpr int SLOT_FLOATS = NACCUM * NC * NPT;  // = NACCUM * 128 * NTOK
     static constexpr int TABLE_INTS = 3 * (MAX_LOCAL + 1);
     static constexpr int RED_BYTES = NPW * NC * 4;
@@ -127,6 +132,31 @@ __device__ __forceinline__ int sk_owner(long long x, long long total, long long 
     while (c > 0 && sk_start(c, total, grid) > x) --c;
     return (int)c;
 }
+
+// Per-CTA work list: q whole units, then one contiguous range of the K-split tail.
+struct SkSched { int NG, q, U0; long long total, grid, t_lo, t_hi; };
+struct SkSeg { int u, gb, ge; bool tail_first; };
+struct SkIter {
+    int i; long long g;
+    __device__ __forceinline__ void reset(const SkSched& s) { i = 0; g = s.t_lo; }
+    __device__ __forceinline__ bool next(const SkSched& s, SkSeg& o) {
+        if (i < s.q) {
+            o.u = i * (int)gridDim.x + (int)blockIdx.x; o.gb = 0; o.ge = s.NG; o.tail_first = false;
+            ++i;
+            return true;
+        }
+        if (g < s.t_hi) {
+            const int ut = (int)(g / s.NG);
+            o.gb = (int)(g - (long long)ut * s.NG);
+            o.ge = (int)min((long long)s.NG, o.gb + (s.t_hi - g));
+            o.u = s.U0 + ut;
+            o.tail_first = (g == s.t_lo);
+            g += o.ge - o.gb;
+            return true;
+        }
+        return false;
+    }
+};
 
 __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
@@ -199,15 +229,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     const uint32_t tmem_base = *s_tmem;
     const uint32_t smem_base = smem_u32(smem);
 
-    // flat schedule: (unit, group) pairs, this CTA's contiguous share
+    // Schedule.  Units are numbered so that the token tiles of one (expert, row tile) are adjacent.
+    // The first q*gridDim.x units run as whole units, round-robin (CTAs that run at the same time
+    // work on adjacent units, so a weight tile shared by several token tiles comes from HBM once and
+    // from L2 afterwards).  The remaining units (fewer than gridDim.x) are cut along K: their
+    // (unit, group) pairs are split into equal contiguous ranges, one per CTA.
     const int NG = (p.KB + C::KPB - 1) / C::KPB;
-    const long long total = (long long)s_tiles[p.num_local] * p.n_mtiles * NG;
-    // with fewer pairs than CTAs only the first `total` CTAs take part, so that every
-    // participating CTA owns at least one pair (the split-unit bookkeeping counts on that)
-    const long long grid = total < (long long)gridDim.x ? (total > 0 ? total : 1) : (long long)gridDim.x;
-    const bool has_work = (long long)blockIdx.x < grid && total > 0;
-    const long long g_lo = has_work ? sk_start(blockIdx.x, total, grid) : 0;
-    const long long g_hi = has_work ? sk_start(blockIdx.x + 1, total, grid) : 0;
+    const int total_units = s_tiles[p.num_local] * p.n_mtiles;
+    SkSched sc;
+    sc.NG = NG;
+    sc.q = total_units / (int)gridDim.x;
+    sc.U0 = sc.q * (int)gridDim.x;
+    sc.total = (long long)(total_units - sc.U0) * NG;
+    // with fewer pairs than CTAs only the first `total` CTAs take part, so that every participating
+    // CTA owns at least one pair (the split-unit bookkeeping counts on that)
+    sc.grid = sc.total < (long long)gridDim.x ? (sc.total > 0 ? sc.total : 1) : (long long)gridDim.x;
+    const bool has_tail = (long long)blockIdx.x < sc.grid && sc.total > 0;
+    sc.t_lo = has_tail ? sk_start(blockIdx.x, sc.total, sc.grid) : 0;
+    sc.t_hi = has_tail ? sk_start(blockIdx.x + 1, sc.total, sc.grid) : 0;
+    const long long total = sc.total, grid = sc.grid;
 
     if (warp < 4) {
     // ================================================================ control warpgroup
@@ -218,10 +258,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             const uint64_t pol = policy_evict_first();
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (long long g = g_lo; g < g_hi && ok;) {
-                const int u = (int)(g / NG), gb = (int)(g - (long long)u * NG);
-                const int ge = (int)min((long long)NG, gb + (g_hi - g));
-                g += ge - gb;
+            SkIter it; it.reset(sc);
+            SkSeg sg;
+            while (ok && it.next(sc, sg)) {
+                const int u = sg.u, gb = sg.gb, ge = sg.ge;
                 Unit un;
                 if (!decode_unit(u, p.n_mtiles, p.num_local, NTOK, s_tiles, s_row0, s_cnt, un)) {
                     atomicCAS(p.status, 0, ERR_BAD_SCHEDULE); break;
@@ -232,7 +272,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, p.status, ERR_WAIT_SMEM_EMPTY)) { ok = false; break; }
                     const uint32_t st = smem_base + stage * C::STAGE_BYTES;
                     const uint32_t full = bar_full + 8 * stage;
-                    mbar_arrive_expect_tx(full, C::TX_BYTES);
+                    mbar_arrive_expect_tx(full, (p.ablate & 4) ? C::NA * C::A_BYTES : C::TX_BYTES);
                     if (p.evict_first_weights) {
                         tma_load_2d_hint(st, &tm_w, kb * 128, wrow, full, pol);
                         if (G1) tma_load_2d_hint(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full, pol);
@@ -240,9 +280,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         tma_load_2d(st, &tm_w, kb * 128, wrow, full);
                         if (G1) tma_load_2d(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full);
                     }
-                    tma_load_2d(st + C::NA * C::A_BYTES, &tm_b0, kb * 128, un.row0, full);
-                    if (!G1) tma_load_2d(st + C::NA * C::A_BYTES + C::B_BYTES, &tm_b1, kb * 128, un.row0, full);
-                    bulk_load(st + C::SC_OFF, p.b_scale + (size_t)kb * p.rows_cap + un.row0, NTOK * 4, full);
+                    if (!(p.ablate & 4)) {
+                        tma_load_2d(st + C::NA * C::A_BYTES, &tm_b0, kb * 128, un.row0, full);
+                        if (!G1) tma_load_2d(st + C::NA * C::A_BYTES + C::B_BYTES, &tm_b1, kb * 128, un.row0, full);
+                        bulk_load(st + C::SC_OFF, p.b_scale + (size_t)kb * p.rows_cap + un.row0, NTOK * 4, full);
+                    }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -259,10 +301,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             int stage = 0; uint32_t phase = 0;
             int ab = 0; uint32_t aphase = 0;
             bool ok = true;
-            for (long long g = g_lo; g < g_hi && ok;) {
-                const int u = (int)(g / NG), gb = (int)(g - (long long)u * NG);
-                const int ge = (int)min((long long)NG, gb + (g_hi - g));
-                g += ge - gb;
+            SkIter it; it.reset(sc);
+            SkSeg sg;
+            while (ok && it.next(sc, sg)) {
+                const int gb = sg.gb, ge = sg.ge;
                 for (int grp = gb; grp < ge && ok; ++grp) {
                     if (!mbar_wait(bar_tempty + 8 * ab, aphase ^ 1, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
                     const int nj = min(C::KPB, p.KB - grp * C::KPB);
@@ -271,7 +313,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         tc_fence_after();
                         const uint32_t st = smem_base + stage * C::STAGE_BYTES;
                         const uint32_t d = tmem_base + ab * C::BUFCOLS + j * C::CPB;
-                        if (G1) {
+                        if (p.ablate & 1) {
+                        } else if (G1) {
                             const uint64_t a_up = make_smem_desc(st);
                             const uint64_t a_gate = make_smem_desc(st + C::A_BYTES);
                             const uint64_t b = make_smem_desc(st + 2 * C::A_BYTES);
@@ -337,11 +380,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             return r;
         };
 
-        for (long long g = g_lo; g < g_hi && ok;) {
-            const int u = (int)(g / NG), gb = (int)(g - (long long)u * NG);
-            const int ge = (int)min((long long)NG, gb + (g_hi - g));
-            const bool first_seg = (g == g_lo);
-            g += ge - gb;
+        SkIter it; it.reset(sc);
+        SkSeg sg;
+        while (ok && it.next(sc, sg)) {
+            const int u = sg.u, gb = sg.gb, ge = sg.ge;
+            const bool first_seg = sg.tail_first;
             Unit un;
             if (!decode_unit(u, p.n_mtiles, p.num_local, NTOK, s_tiles, s_row0, s_cnt, un)) break;
 #pragma unroll
@@ -361,24 +404,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     sw[j][0] = __ldg(ws0 + kb);
                     if (G1) sw[j][1] = __ldg(ws1 + kb);
                 }
+                const int st0 = stage;
+                float scr[C::EARLY_SCALES ? C::KPB : 1][C::EARLY_SCALES ? C::NC : 1];
+                if (C::EARLY_SCALES && !(p.ablate & 2)) {
+#pragma unroll
+                    for (int j = 0; j < C::KPB; ++j) {
+                        if (j < nj) {
+                            int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
+                            const uint32_t ph = (st0 + j >= C::STAGES) ? (phase ^ 1) : phase;
+                            if (!mbar_wait(bar_full + 8 * sj, ph, p.status, ERR_WAIT_SMEM_FULL)) ok = false;
+                            const float* scp = reinterpret_cast<const float*>(smem + sj * C::STAGE_BYTES + C::SC_OFF) + c0;
+#pragma unroll
+                            for (int i = 0; i < C::NC; i += 4) {
+                                const float4 s4 = *reinterpret_cast<const float4*>(scp + i);
+                                scr[j][i] = s4.x; scr[j][i + 1] = s4.y; scr[j][i + 2] = s4.z; scr[j][i + 3] = s4.w;
+                            }
+                        }
+                    }
+                    if (!ok) break;
+                    __syncwarp();
+                    if (lane == 0) {
+                        for (int j = 0; j < nj; ++j) {
+                            int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
+                            mbar_arrive(bar_empty + 8 * sj);
+                        }
+                    }
+                }
                 if (!mbar_wait(bar_tfull + 8 * ab, aphase, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t tbuf = tmem_base + tlane + ab * C::BUFCOLS + c0;
 
-                // flattened chunk list (j, column chunk, accumulator); the tcgen05.ld of chunk k+1 is in
-                // flight while chunk k is folded into the accumulators
+                // flattened chunk list (K block, column chunk, accumulator, partial); the tcgen05.ld of
+                // chunk k+1 is in flight while chunk k is folded into the accumulators
                 constexpr int NCH = C::NC / C::CH;
                 constexpr int NK = C::KPB * NCH * C::NACCUM * C::NSPLIT;
                 float part[2][C::CH];
-                tmem_ld_chunk<C::CH>(tbuf, part[0]);
-                const int st0 = stage;
+                if (!(p.ablate & 2)) tmem_ld_chunk<C::CH>(tbuf, part[0]);
 #pragma unroll
                 for (int k = 0; k < NK; ++k) {
                     const int sp = k % C::NSPLIT;
                     const int a = (k / C::NSPLIT) % C::NACCUM;
                     const int ch = (k / (C::NSPLIT * C::NACCUM)) % NCH;
                     const int j = k / (C::NSPLIT * C::NACCUM * NCH);
-                    if (j < nj) {
+                    if (j < nj && !(p.ablate & 2)) {
                         tmem_wait_ld();
                         if (k + 1 < NK) {
                             const int sp1 = (k + 1) % C::NSPLIT;
@@ -389,23 +457,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                                 tmem_ld_chunk<C::CH>(tbuf + j1 * C::CPB + (a1 * C::NSPLIT + sp1) * NTOK + ch1 * C::CH,
                                                      part[(k + 1) & 1]);
                         }
-                        int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
-                        if (ch == 0 && a == 0 && sp == 0) {
-                            // token scales of this K block arrived with the stage's transaction barrier
-                            const uint32_t ph = (st0 + j >= C::STAGES) ? (phase ^ 1) : phase;
-                            if (!mbar_wait(bar_full + 8 * sj, ph, p.status, ERR_WAIT_SMEM_FULL)) ok = false;
-                        }
-                        const float* sc = reinterpret_cast<const float*>(smem + sj * C::STAGE_BYTES + C::SC_OFF) + c0 + ch * C::CH;
                         const float swa = sw[j][a];
+                        if (C::EARLY_SCALES) {
 #pragma unroll
-                        for (int i = 0; i < C::CH; i += 4) {
-                            const float4 s4 = *reinterpret_cast<const float4*>(sc + i);
-                            const float2 m0 = __fmul2_rn(make_float2(s4.x, s4.y), make_float2(swa, swa));
-                            const float2 m1 = __fmul2_rn(make_float2(s4.z, s4.w), make_float2(swa, swa));
-                            float* ac = &acc[a][ch * C::CH + i];
-                            const float2 r0 = __ffma2_rn(make_float2(part[k & 1][i], part[k & 1][i + 1]), m0, make_float2(ac[0], ac[1]));
-                            const float2 r1 = __ffma2_rn(make_float2(part[k & 1][i + 2], part[k & 1][i + 3]), m1, make_float2(ac[2], ac[3]));
-                            ac[0] = r0.x; ac[1] = r0.y; ac[2] = r1.x; ac[3] = r1.y;
+                            for (int i = 0; i < C::CH; i += 2) {
+                                const float2 mm = __fmul2_rn(make_float2(scr[j][ch * C::CH + i], scr[j][ch * C::CH + i + 1]),
+                                                             make_float2(swa, swa));
+                                float* ac = &acc[a][ch * C::CH + i];
+                                const float2 r0 = __ffma2_rn(make_float2(part[k & 1][i], part[k & 1][i + 1]), mm,
+                                                             make_float2(ac[0], ac[1]));
+                                ac[0] = r0.x; ac[1] = r0.y;
+                            }
+                        } else {
+                            int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
+                            if (ch == 0 && a == 0 && sp == 0) {
+                                // token scales of this K block arrived with the stage's transaction barrier
+                                const uint32_t ph = (st0 + j >= C::STAGES) ? (phase ^ 1) : phase;
+                                if (!mbar_wait(bar_full + 8 * sj, ph, p.status, ERR_WAIT_SMEM_FULL)) ok = false;
+                            }
+                            const float* scp = reinterpret_cast<const float*>(smem + sj * C::STAGE_BYTES + C::SC_OFF) + c0 + ch * C::CH;
+#pragma unroll
+                            for (int i = 0; i < C::CH; i += 4) {
+                                const float4 s4 = *reinterpret_cast<const float4*>(scp + i);
+                                const float2 m0 = __fmul2_rn(make_float2(s4.x, s4.y), make_float2(swa, swa));
+                                const float2 m1 = __fmul2_rn(make_float2(s4.z, s4.w), make_float2(swa, swa));
+                                float* ac = &acc[a][ch * C::CH + i];
+                                const float2 r0 = __ffma2_rn(make_float2(part[k & 1][i], part[k & 1][i + 1]), m0, make_float2(ac[0], ac[1]));
+                                const float2 r1 = __ffma2_rn(make_float2(part[k & 1][i + 2], part[k & 1][i + 3]), m1, make_float2(ac[2], ac[3]));
+                                ac[0] = r0.x; ac[1] = r0.y; ac[2] = r1.x; ac[3] = r1.y;
+                            }
                         }
                     }
                 }
@@ -415,9 +495,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(bar_tempty + 8 * ab);
-                    for (int j = 0; j < nj; ++j) {
-                        int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
-                        mbar_arrive(bar_empty + 8 * sj);
+                    if (!C::EARLY_SCALES || (p.ablate & 2)) {
+                        for (int j = 0; j < nj; ++j) {
+                            int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
+                            mbar_arrive(bar_empty + 8 * sj);
+                        }
                     }
                 }
                 stage += nj;
@@ -428,7 +510,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 
             if (!(gb == 0 && ge == NG)) {
                 // ---- split unit: publish the partial, the last CTA to arrive adds them up in CTA order
-                const long long u0 = (long long)u * NG;
+                const long long u0 = (long long)(u - sc.U0) * NG;      // tail-relative flat index of the unit's first pair
                 const int c_first = sk_owner(u0, total, grid), c_last = sk_owner(u0 + NG - 1, total, grid);
                 float* slot = p.sk_partial + (size_t)(blockIdx.x * 2 + (first_seg ? 0 : 1)) * SK_SLOT_FLOATS_MAX;
 #pragma unroll
@@ -450,7 +532,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                     for (int i = 0; i < C::NC; ++i) acc[a][i] = 0.f;
                 for (int c = c_first; c <= c_last; ++c) {
-                    const bool c_first_seg = (int)(sk_start(c, total, grid) / NG) == u;
+                    const bool c_first_seg = (int)(sk_start(c, total, grid) / NG) == u - sc.U0;
                     const float* src = p.sk_partial + (size_t)(c * 2 + (c_first_seg ? 0 : 1)) * SK_SLOT_FLOATS_MAX;
 #pragma unroll
                     for (int a = 0; a < C::NACCUM; ++a)
