@@ -52,6 +52,30 @@ EncodeTiledFn get_encode() {
     return fn;
 }
 
+// All kernels of a forward are launched with programmatic stream serialization (unless
+// B200MOE_PDL=0): the next kernel's prologue overlaps the tail of the one before, and each
+// kernel calls griddepcontrol.wait before it touches anything an earlier kernel wrote.
+// B200MOE_PDL is a bit mask over the launch sites (1 route/count, 2 permute, 4 gather, 8 GEMM1,
+// 16 GEMM2, 32 combine); default: all.
+enum : int { PDL_ROUTE = 1, PDL_PERMUTE = 2, PDL_GATHER = 4, PDL_GEMM1 = 8, PDL_GEMM2 = 16, PDL_COMBINE = 32 };
+int pdl_mask() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("B200MOE_PDL"); v = e ? atoi(e) : 63; }
+    return v;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_k(int site, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                     Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = (pdl_mask() & site) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 // 2-D byte tensor [rows][cols] (cols contiguous), box [box_rows][128 bytes], 128-byte swizzle.
 int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
     EncodeTiledFn enc = get_encode();
@@ -129,8 +153,8 @@ cudaError_t set_attr() {
 template <int NTOK, bool G1>
 cudaError_t launch_gemm(int grid, cudaStream_t st, const CUtensorMap& w, const CUtensorMap& b0, const CUtensorMap& b1,
                         const GemmParams& p) {
-    gemm_kernel<NTOK, G1><<<grid, GemmCfg<NTOK, G1>::NTHREADS, GemmCfg<NTOK, G1>::SMEM_BYTES, st>>>(w, b0, b1, p);
-    return cudaGetLastError();
+    return launch_k(G1 ? PDL_GEMM1 : PDL_GEMM2, gemm_kernel<NTOK, G1>, dim3(grid), dim3(GemmCfg<NTOK, G1>::NTHREADS),
+                    GemmCfg<NTOK, G1>::SMEM_BYTES, st, w, b0, b1, p);
 }
 
 template <bool G1>
@@ -170,11 +194,11 @@ template <int MODE>
 cudaError_t launch_route(int vpt, const RouteParams& rp, cudaStream_t st) {
     const int grid = (rp.T + 7) / 8;
     switch (vpt) {
-        case 1: route_kernel<1, MODE><<<grid, 256, 0, st>>>(rp); break;
-        case 2: route_kernel<2, MODE><<<grid, 256, 0, st>>>(rp); break;
-        case 4: route_kernel<4, MODE><<<grid, 256, 0, st>>>(rp); break;
-        case 8: route_kernel<8, MODE><<<grid, 256, 0, st>>>(rp); break;
-        default: route_kernel<16, MODE><<<grid, 256, 0, st>>>(rp); break;
+        case 1: return launch_k(PDL_ROUTE, route_kernel<1, MODE>, dim3(grid), dim3(256), 0, st, rp);
+        case 2: return launch_k(PDL_ROUTE, route_kernel<2, MODE>, dim3(grid), dim3(256), 0, st, rp);
+        case 4: return launch_k(PDL_ROUTE, route_kernel<4, MODE>, dim3(grid), dim3(256), 0, st, rp);
+        case 8: return launch_k(PDL_ROUTE, route_kernel<8, MODE>, dim3(grid), dim3(256), 0, st, rp);
+        default: return launch_k(PDL_ROUTE, route_kernel<16, MODE>, dim3(grid), dim3(256), 0, st, rp);
     }
     return cudaGetLastError();
 }
@@ -227,22 +251,22 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     pp.topk_idx = topk_idx; pp.topk_w = topk_w; pp.status = status; pp.counts = counts;
     pp.expert_row0 = row0; pp.tile_prefix = tiles; pp.pair_row = pair_row; pp.row_token = row_token;
     pp.row_w = row_w; pp.rows_cap = rows_cap;
-    permute_kernel<<<El, 256, 0, st>>>(pp);
-    CU_TRY(cudaGetLastError());
+    CU_TRY(launch_k(PDL_PERMUTE, permute_kernel, dim3(El), dim3(256), 0, st, pp));
     CU_TRY(prof_mark(h, 2, st));
 
     const long long max_rows = (long long)T * (c.top_k < El ? c.top_k : El) + (long long)ROW_ALIGN * El;
     int ggrid = (int)((max_rows + 7) / 8);
     if (ggrid > h->num_sms * 8) ggrid = h->num_sms * 8;
-    gather_kernel<<<ggrid, 256, 0, st>>>(static_cast<const uint8_t*>(hidden), static_cast<const float*>(hidden_scale),
-                                         row_token, status, a_perm, a_scale, T, H, rows_cap);
-    CU_TRY(cudaGetLastError());
+    CU_TRY(launch_k(PDL_GATHER, gather_kernel, dim3(ggrid), dim3(256), 0, st, static_cast<const uint8_t*>(hidden),
+                    static_cast<const float*>(hidden_scale), (const int32_t*)row_token, (const int*)status, a_perm,
+                    a_scale, T, H, rows_cap));
     CU_TRY(prof_mark(h, 3, st));
 
     GemmParams g1;
     memset(&g1, 0, sizeof(g1));
     g1.status = status; g1.counts = counts; g1.expert_row0 = row0; g1.tile_prefix = tiles; g1.num_local = El;
     g1.KB = H / 128; g1.n_mtiles = I / 128; g1.rows_per_expert = 2 * I; g1.gate_offset = I; g1.scale_rows = 2 * I / 128;
+    g1.unit_rows = 128; g1.valid_rows = 2 * I;
     g1.w_scale = static_cast<const float*>(s13); g1.b_scale = a_scale; g1.rows_cap = rows_cap;
     g1.act_hi = act_hi; g1.act_lo = act_lo; g1.act_scale = act_scale; g1.I = I; g1.H = H;
     static int evf = -1;
@@ -257,7 +281,8 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     GemmParams g2;
     memset(&g2, 0, sizeof(g2));
     g2.status = status; g2.counts = counts; g2.expert_row0 = row0; g2.tile_prefix = tiles; g2.num_local = El;
-    g2.KB = I / 128; g2.n_mtiles = H / 128; g2.rows_per_expert = H; g2.gate_offset = 0; g2.scale_rows = H / 128;
+    g2.KB = I / 128; g2.n_mtiles = (H + 255) / 256; g2.rows_per_expert = H; g2.gate_offset = 128; g2.scale_rows = H / 128;
+    g2.unit_rows = 256; g2.valid_rows = H;
     g2.w_scale = static_cast<const float*>(s2); g2.b_scale = act_scale; g2.rows_cap = rows_cap;
     g2.row_w = row_w; g2.y = y; g2.H = H; g2.I = I;
     g2.evict_first_weights = evf && ntok < 128;
@@ -269,10 +294,11 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
 
     const int cgrid = T < h->num_sms * 8 ? T : h->num_sms * 8;
     if (out_bf16)
-        combine_kernel<true><<<cgrid, 256, 0, st>>>(y, topk_idx, pair_row, out, T, H, c.top_k, local_offset, El);
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<true>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
+                        (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El));
     else
-        combine_kernel<false><<<cgrid, 256, 0, st>>>(y, topk_idx, pair_row, out, T, H, c.top_k, local_offset, El);
-    CU_TRY(cudaGetLastError());
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<false>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
+                        (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El));
     CU_TRY(prof_mark(h, 6, st));
     if (h->prof_slots) ++h->prof_calls;
     return 0;

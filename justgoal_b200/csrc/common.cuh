@@ -30,6 +30,15 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
     return t;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it on the stream still runs; pdl_wait() blocks until that kernel has completed
+// and its writes are visible (everything before it may only touch memory the previous kernel
+// does not write); pdl_launch() lets the NEXT kernel on the stream begin its own prologue.
+// Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));

@@ -44,7 +44,9 @@ struct GemmParams {
     int KB;               // K blocks of 128
     int n_mtiles;         // 128-row weight tiles per expert that one unit family covers
     int rows_per_expert;  // rows of the weight matrix per expert (2I for GEMM1, H for GEMM2)
-    int gate_offset;      // GEMM1: row offset of the gate half (I)
+    int gate_offset;      // row offset of the unit's second weight tile (GEMM1: I, the gate half; GEMM2: 128)
+    int unit_rows;        // weight rows one unit advances by (GEMM1: 128, GEMM2: 256)
+    int valid_rows;       // GEMM2: output columns H (the last unit's second tile may lie beyond)
     int scale_rows;       // weight-scale rows per expert (rows_per_expert / 128)
     const float* w_scale; // [E_local, scale_rows, KB]
     const float* b_scale; // [KB, rows_cap] token-side scales
@@ -60,7 +62,7 @@ struct GemmParams {
 
 template <int NTOK, bool G1>
 struct GemmCfg {
-    static constexpr int NA = G1 ? 2 : 1;                 // weight tiles per stage
+    static constexpr int NA = 2;                          // weight tiles per stage (GEMM1: up + gate rows; GEMM2: two row tiles)
     static constexpr int NB = G1 ? 1 : 2;                 // token tiles per stage
     static constexpr int A_BYTES = 128 * 128;
     static constexpr int B_BYTES = NTOK * 128;
@@ -69,11 +71,11 @@ struct GemmCfg {
     static constexpr int TX_BYTES = NA * A_BYTES + NB * B_BYTES + NTOK * 4;
     static constexpr int STAGES_RAW = (208 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int NACCUM = G1 ? 2 : 1;
+    static constexpr int NACCUM = 2;                      // one accumulator per weight tile
     // Dependent MMAs into one accumulator serialise on the tensor pipe's latency, which dominates
     // for narrow token tiles; the MMAs of one K block are therefore spread over NSPLIT independent
-    // partial accumulators (GEMM1: even/odd K step; GEMM2: hi/lo x even/odd) that the promotion adds.
-    static constexpr int NSPLIT = G1 ? (NTOK <= 32 ? 2 : 1) : (NTOK <= 32 ? 4 : (NTOK == 64 ? 2 : 1));
+    // partial accumulators (GEMM1: even/odd K step; GEMM2: hi / lo operand) that the promotion adds.
+    static constexpr int NSPLIT = NTOK <= 32 ? 2 : 1;
     static constexpr int CPB = NACCUM * NSPLIT * NTOK;     // TMEM columns per K block
     static constexpr int KPB = (128 / CPB) < 1 ? 1 : (128 / CPB);
     static constexpr int BUFCOLS = KPB * CPB;               // TMEM columns per hand-off buffer
@@ -218,6 +220,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         if (!G1) tma_prefetch_desc(&tm_b1);
     }
     if (warp == 1) { tmem_alloc(smem_u32(s_tmem), C::TMEM_COLS); tmem_relinquish(); }
+    // everything above touches only this CTA's shared memory and TMEM; the tables below are
+    // written by the kernels before this one
+    pdl_wait();
+    pdl_launch();
     for (int i = threadIdx.x; i <= p.num_local; i += blockDim.x) {
         s_tiles[i] = p.tile_prefix[i];
         s_row0[i] = p.expert_row0[i];
@@ -266,7 +272,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 if (!decode_unit(u, p.n_mtiles, p.num_local, NTOK, s_tiles, s_row0, s_cnt, un)) {
                     atomicCAS(p.status, 0, ERR_BAD_SCHEDULE); break;
                 }
-                const int wrow = un.e * p.rows_per_expert + un.mt * 128;
+                const int wrow = un.e * p.rows_per_expert + un.mt * p.unit_rows;
                 const int kb_end = min(p.KB, ge * C::KPB);
                 for (int kb = gb * C::KPB; kb < kb_end; ++kb) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, p.status, ERR_WAIT_SMEM_EMPTY)) { ok = false; break; }
@@ -275,10 +281,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     mbar_arrive_expect_tx(full, (p.ablate & 4) ? C::NA * C::A_BYTES : C::TX_BYTES);
                     if (p.evict_first_weights) {
                         tma_load_2d_hint(st, &tm_w, kb * 128, wrow, full, pol);
-                        if (G1) tma_load_2d_hint(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full, pol);
+                        tma_load_2d_hint(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full, pol);
                     } else {
                         tma_load_2d(st, &tm_w, kb * 128, wrow, full);
-                        if (G1) tma_load_2d(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full);
+                        tma_load_2d(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full);
                     }
                     if (!(p.ablate & 4)) {
                         tma_load_2d(st + C::NA * C::A_BYTES, &tm_b0, kb * 128, un.row0, full);
@@ -325,22 +331,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                                 umma_f8(d + (C::NSPLIT + sp) * NTOK, a_gate + 2 * k, b + 2 * k, idesc, k >= C::NSPLIT);
                             }
                         } else {
-                            const uint64_t a = make_smem_desc(st);
-                            const uint64_t bh = make_smem_desc(st + C::A_BYTES);
-                            const uint64_t bl = make_smem_desc(st + C::A_BYTES + C::B_BYTES);
-                            if (C::NSPLIT == 1) {
+                            const uint64_t a0 = make_smem_desc(st);
+                            const uint64_t a1 = make_smem_desc(st + C::A_BYTES);
+                            const uint64_t bh = make_smem_desc(st + 2 * C::A_BYTES);
+                            const uint64_t bl = make_smem_desc(st + 2 * C::A_BYTES + C::B_BYTES);
+                            // tile t, operand half o (hi, lo): partial accumulator o when NSPLIT == 2, else both into one
 #pragma unroll
-                                for (int k = 0; k < 4; ++k) umma_f8(d, a + 2 * k, bh + 2 * k, idesc, k > 0);
+                            for (int k = 0; k < 4; ++k) {
+                                umma_f8(d, a0 + 2 * k, bh + 2 * k, idesc, k > 0);
+                                umma_f8(d + C::NSPLIT * NTOK, a1 + 2 * k, bh + 2 * k, idesc, k > 0);
+                            }
 #pragma unroll
-                                for (int k = 0; k < 4; ++k) umma_f8(d, a + 2 * k, bl + 2 * k, idesc, 1);
-                            } else {
-                                constexpr int HS = C::NSPLIT / 2;      // partial accumulators per operand half
-#pragma unroll
-                                for (int k = 0; k < 4; ++k) {
-                                    const int sp = k % HS;
-                                    umma_f8(d + sp * NTOK, a + 2 * k, bh + 2 * k, idesc, k >= HS);
-                                    umma_f8(d + (HS + sp) * NTOK, a + 2 * k, bl + 2 * k, idesc, k >= HS);
-                                }
+                            for (int k = 0; k < 4; ++k) {
+                                umma_f8(d + (C::NSPLIT - 1) * NTOK, a0 + 2 * k, bl + 2 * k, idesc, C::NSPLIT == 1 || k > 0);
+                                umma_f8(d + (2 * C::NSPLIT - 1) * NTOK, a1 + 2 * k, bl + 2 * k, idesc, C::NSPLIT == 1 || k > 0);
                             }
                         }
                         umma_commit(bar_empty + 8 * stage);
@@ -391,8 +395,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             for (int a = 0; a < C::NACCUM; ++a)
 #pragma unroll
                 for (int i = 0; i < C::NC; ++i) acc[a][i] = 0.f;
-            const float* ws0 = p.w_scale + ((size_t)un.e * p.scale_rows + un.mt) * p.KB;
-            const float* ws1 = G1 ? ws0 + (size_t)(p.gate_offset >> 7) * p.KB : ws0;
+            // weight-scale rows of the unit's two tiles (the second one of GEMM2's last unit may not exist)
+            const int srow0 = un.mt * (p.unit_rows >> 7);
+            const int srow1 = min(srow0 + (p.gate_offset >> 7), p.scale_rows - 1);
+            const float* ws0 = p.w_scale + ((size_t)un.e * p.scale_rows + srow0) * p.KB;
+            const float* ws1 = p.w_scale + ((size_t)un.e * p.scale_rows + srow1) * p.KB;
 
             for (int grp = gb; grp < ge; ++grp) {
                 const int kb0 = grp * C::KPB;
@@ -402,7 +409,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 for (int j = 0; j < C::KPB; ++j) {
                     const int kb = min(kb0 + j, p.KB - 1);
                     sw[j][0] = __ldg(ws0 + kb);
-                    if (G1) sw[j][1] = __ldg(ws1 + kb);
+                    sw[j][1] = __ldg(ws1 + kb);
                 }
                 const int st0 = stage;
                 float scr[C::EARLY_SCALES ? C::KPB : 1][C::EARLY_SCALES ? C::NC : 1];
@@ -582,13 +589,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 }
                 if (!group_sync()) { ok = false; break; }          // s_red is reused by the next unit
             } else {
-                const size_t col = (size_t)un.mt * 128 + m;
+                const int col0 = un.mt * p.unit_rows + m;
+                const bool second = col0 + p.gate_offset < p.valid_rows;
 #pragma unroll
                 for (int i = 0; i < C::NC; ++i) {
                     const int c = c0 + i;
                     if (c < un.nvalid) {
                         const size_t row = (size_t)(un.row0 + c);
-                        p.y[row * p.H + col] = acc[0][i] * __ldg(p.row_w + row);
+                        const float w = __ldg(p.row_w + row);
+                        p.y[row * p.H + col0] = acc[0][i] * w;
+                        if (second) p.y[row * p.H + col0 + p.gate_offset] = acc[1][i] * w;
                     }
                 }
             }

@@ -37,6 +37,8 @@ struct PlanParams {
 // routing ran on another rank).
 __global__ void count_kernel(const int32_t* __restrict__ topk_idx, int n, int local_offset, int num_local,
                              int* __restrict__ counts) {
+    pdl_wait();
+    pdl_launch();
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const int le = topk_idx[i] - local_offset;
         if (le >= 0 && le < num_local) atomicAdd(counts + le, 1);
@@ -50,6 +52,8 @@ __global__ void __launch_bounds__(256) permute_kernel(const PlanParams p) {
     __shared__ int s_tiles[MAX_LOCAL + 1];
     __shared__ int s_scan[256];
     const int e = blockIdx.x, tid = threadIdx.x;
+    pdl_wait();
+    pdl_launch();
 
     if (tid < 32) {
         // warp-parallel exclusive scan over the (<= 256) counts: lane l owns experts [l*per, (l+1)*per)
@@ -139,6 +143,8 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__
                                                      const int32_t* __restrict__ row_token, const int* __restrict__ status,
                                                      uint8_t* __restrict__ a_perm, float* __restrict__ a_scale_perm,
                                                      int T, int H, int rows_cap) {
+    pdl_wait();
+    pdl_launch();
     const int rows = status[ST_ROWS];
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -166,6 +172,8 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
                                                       int T, int H, int top_k, int local_offset, int num_local) {
     __shared__ int s_rows[8];
     __shared__ int s_n;
+    pdl_wait();
+    pdl_launch();
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
         __syncthreads();
         if (threadIdx.x < 32) {

@@ -37,6 +37,8 @@ template <int VPT, int MODE>
 __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_wait();
+    pdl_launch();
     if (t >= p.T) return;
     const unsigned FULL = 0xFFFFFFFFu;
 
