@@ -70,6 +70,10 @@ typedef struct b200moe_ws_layout {
     size_t y;             /* float[rows_cap, H] weighted expert outputs per row            */
     size_t sk_count;      /* int32[2][2*SMs] arrival counters of K-split units (GEMM1, GEMM2)*/
     size_t sk_partial;    /* float[2*SMs][32768] fp32 partial accumulators of K-split units */
+    size_t trace;         /* int64[2][SMs][16] per-CTA time lines of GEMM1 and GEMM2: slot 0 =
+                             %globaltimer at entry, slots 1..11 = SM clocks since entry at:
+                             prologue done, first/last TMA issue, first/last MMA, first/last
+                             promotion, partial published, partials added, epilogue, exit     */
     size_t rows_cap;      /* number of rows the row-indexed buffers hold                   */
     size_t token_tile;    /* tokens per GEMM tile chosen for this T                        */
     size_t total_bytes;

@@ -16,6 +16,7 @@
 
 #include "../../include/b200moe.h"
 #include "common.cuh"
+#include "front.cuh"
 #include "gemm.cuh"
 #include "permute.cuh"
 #include "routing.cuh"
@@ -64,6 +65,12 @@ int pdl_mask() {
     return v;
 }
 
+// Measured: with thousands of tokens the early-resident dependents slow the front kernels down
+// (2.17 ms against 1.93 ms at T=4096), with a few dozen tokens the overlap saves ~9 us per forward.
+// So the forward turns the attribute on only for small token counts (a shape-only decision).
+thread_local int g_call_pdl = 0;
+inline void set_call_pdl(int num_tokens) { g_call_pdl = num_tokens <= 512 ? pdl_mask() : 0; }
+
 template <typename... KArgs, typename... Args>
 cudaError_t launch_k(int site, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                      Args&&... args) {
@@ -72,7 +79,7 @@ cudaError_t launch_k(int site, void (*kern)(KArgs...), dim3 grid, dim3 block, si
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = (pdl_mask() & site) ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = (g_call_pdl & site) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
@@ -139,6 +146,7 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     L->act_scale = take((size_t)(c.intermediate / 128) * rows * 4);
     L->y = take(rows * c.hidden * 4);
     L->sk_partial = take((size_t)2 * h->num_sms * SK_SLOT_FLOATS_MAX * 4);
+    L->trace = take((size_t)2 * h->num_sms * TRACE_SLOTS * 8);   // [GEMM1 | GEMM2][CTA][slot]
     L->rows_cap = rows;
     L->token_tile = (size_t)pick_token_tile(c, T);
     L->total_bytes = off;
@@ -220,7 +228,8 @@ inline cudaError_t prof_mark(b200moe_ctx* h, int point, cudaStream_t st) {
 // Everything after routing: permute -> gather -> GEMM1 -> GEMM2 -> combine.
 int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
                 const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2, int T,
-                int local_offset, void* out, bool out_bf16, uint8_t* ws, const b200moe_ws_layout& L, cudaStream_t st) {
+                int local_offset, void* out, bool out_bf16, uint8_t* ws, const b200moe_ws_layout& L, cudaStream_t st,
+                bool fused_front = false) {
     const b200moe_config& c = h->cfg;
     const int El = c.num_local_experts, H = c.hidden, I = c.intermediate;
     const int ntok = (int)L.token_tile, rows_cap = (int)L.rows_cap;
@@ -251,16 +260,28 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     pp.topk_idx = topk_idx; pp.topk_w = topk_w; pp.status = status; pp.counts = counts;
     pp.expert_row0 = row0; pp.tile_prefix = tiles; pp.pair_row = pair_row; pp.row_token = row_token;
     pp.row_w = row_w; pp.rows_cap = rows_cap;
-    CU_TRY(launch_k(PDL_PERMUTE, permute_kernel, dim3(El), dim3(256), 0, st, pp));
-    CU_TRY(prof_mark(h, 2, st));
+    if (fused_front) {
+        // small token counts: histogram + permutation + gather in one launch (front.cuh)
+        FrontParams fp;
+        fp.plan = pp;
+        fp.hidden = static_cast<const uint8_t*>(hidden); fp.hscale = static_cast<const float*>(hidden_scale);
+        fp.a_perm = a_perm; fp.a_scale_perm = a_scale; fp.H = H;
+        const int fgrid = h->num_sms < 32 ? h->num_sms : 32;
+        CU_TRY(launch_k(PDL_PERMUTE, front_small_kernel, dim3(fgrid), dim3(FRONT_THREADS), 0, st, fp));
+        CU_TRY(prof_mark(h, 2, st));
+        CU_TRY(prof_mark(h, 3, st));
+    } else {
+        CU_TRY(launch_k(PDL_PERMUTE, permute_kernel, dim3(El), dim3(256), 0, st, pp));
+        CU_TRY(prof_mark(h, 2, st));
 
-    const long long max_rows = (long long)T * (c.top_k < El ? c.top_k : El) + (long long)ROW_ALIGN * El;
-    int ggrid = (int)((max_rows + 7) / 8);
-    if (ggrid > h->num_sms * 8) ggrid = h->num_sms * 8;
-    CU_TRY(launch_k(PDL_GATHER, gather_kernel, dim3(ggrid), dim3(256), 0, st, static_cast<const uint8_t*>(hidden),
-                    static_cast<const float*>(hidden_scale), (const int32_t*)row_token, (const int*)status, a_perm,
-                    a_scale, T, H, rows_cap));
-    CU_TRY(prof_mark(h, 3, st));
+        const long long max_rows = (long long)T * (c.top_k < El ? c.top_k : El) + (long long)ROW_ALIGN * El;
+        int ggrid = (int)((max_rows + 7) / 8);
+        if (ggrid > h->num_sms * 8) ggrid = h->num_sms * 8;
+        CU_TRY(launch_k(PDL_GATHER, gather_kernel, dim3(ggrid), dim3(256), 0, st, static_cast<const uint8_t*>(hidden),
+                        static_cast<const float*>(hidden_scale), (const int32_t*)row_token, (const int*)status, a_perm,
+                        a_scale, T, H, rows_cap));
+        CU_TRY(prof_mark(h, 3, st));
+    }
 
     GemmParams g1;
     memset(&g1, 0, sizeof(g1));
@@ -275,6 +296,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g1.sk_count = reinterpret_cast<int*>(ws + L.sk_count);
     g1.sk_partial = reinterpret_cast<float*>(ws + L.sk_partial);
     g1.ablate = h->ablate & 0xFF;
+    g1.trace = reinterpret_cast<long long*>(ws + L.trace);
     CU_TRY(launch_gemm_ntok<true>(ntok, h->num_sms, st, m_w13, m_a, m_a, g1));
     CU_TRY(prof_mark(h, 4, st));
 
@@ -289,6 +311,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g2.sk_count = reinterpret_cast<int*>(ws + L.sk_count) + 2 * h->num_sms;
     g2.sk_partial = g1.sk_partial;
     g2.ablate = (h->ablate >> 8) & 0xFF;
+    g2.trace = g1.trace + (size_t)h->num_sms * TRACE_SLOTS;
     CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
     CU_TRY(prof_mark(h, 5, st));
 
@@ -403,7 +426,8 @@ int b200moe_workspace_bytes(b200moe_handle h, int num_tokens, size_t* bytes) {
 
 int b200moe_launches_per_forward(b200moe_handle h, int num_tokens, int* launches) {
     if (!h || !launches || num_tokens < 0) return B200MOE_E_BADARG;
-    *launches = num_tokens == 0 ? 0 : 6;   // route, permute, gather, gemm1, gemm2, combine
+    // route, [permute, gather | fused permute+gather for small T], gemm1, gemm2, combine
+    *launches = num_tokens == 0 ? 0 : (num_tokens <= FRONT_MAX_T ? 5 : 6);
     return 0;
 }
 
@@ -435,6 +459,7 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     const b200moe_config& c = h->cfg;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
+    set_call_pdl(T);
     // status + counts are contiguous at the head of the workspace: one memset clears both
     CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
     CU_TRY(prof_mark(h, 0, st));
@@ -444,10 +469,12 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     rp.local_offset = local_offset; rp.num_local = c.num_local_experts; rp.scale = scale;
     rp.topk_idx = reinterpret_cast<int32_t*>(ws + L.topk_idx); rp.topk_w = reinterpret_cast<float*>(ws + L.topk_w);
     rp.counts = reinterpret_cast<int*>(ws + L.counts);
+    const bool fused = T <= FRONT_MAX_T;
+    if (fused) rp.counts = nullptr;       // the fused kernel builds the histogram itself
     CU_TRY(do_route(c, rp, st));
     CU_TRY(prof_mark(h, 1, st));
     return run_experts(h, rp.topk_idx, rp.topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output,
-                       true, ws, L, st);
+                       true, ws, L, st, fused);
 }
 
 int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
@@ -464,6 +491,7 @@ int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const floa
     const b200moe_config& c = h->cfg;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
+    set_call_pdl(T);
     CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
     CU_TRY(prof_mark(h, 0, st));
     const int n = T * c.top_k;

@@ -1,0 +1,111 @@
+// Fused permutation + gather for small token counts (T <= FRONT_MAX_T): histogram, scan, stable
+// permutation and the expert-sorted activation gather in ONE launch after the routing kernel.
+//
+// With a few dozen tokens the separate kernels are pure launch latency, so every CTA of this
+// kernel redoes the (tiny, integer) histogram and permutation for ALL tokens in its own shared
+// memory - no CTA ever waits for another - and then copies its share of the rows.  CTA 0 alone
+// writes the tables that later kernels read (counts, row maps); all CTAs derive identical values.
+// Same results as count_kernel + permute_kernel + gather_kernel (permute.cuh); the reference
+// fuses the same stages for small batches
+// (kda05_reproduction_full_shape/fable-5.1/moe_fp8_fwd/<def>/fable51_moe_v94/kernel.cu:724-806).
+#pragma once
+#include "permute.cuh"
+#include "routing.cuh"
+
+namespace b200moe {
+
+constexpr int FRONT_MAX_T = 128;
+constexpr int FRONT_MAX_ROWS = FRONT_MAX_T * 8 + ROW_ALIGN * MAX_LOCAL;   // worst case incl. segment padding
+constexpr int FRONT_THREADS = 1024;
+
+struct FrontParams {
+    PlanParams plan;              // topk_idx / topk_w in, tables to publish (CTA 0) out
+    const uint8_t* hidden;        // [T, H] fp8
+    const float* hscale;          // [H/128, T]
+    uint8_t* a_perm;              // [rows_cap, H]
+    float* a_scale_perm;          // [H/128, rows_cap]
+    int H;
+};
+
+__global__ void __launch_bounds__(FRONT_THREADS, 1) front_small_kernel(const FrontParams fp) {
+    __shared__ int s_idx[FRONT_MAX_T * 8];
+    __shared__ float s_w[FRONT_MAX_T * 8];
+    __shared__ int s_cnt[MAX_LOCAL];
+    __shared__ int s_row0[MAX_LOCAL + 1];
+    __shared__ int s_tiles[MAX_LOCAL + 1];
+    __shared__ int s_row_token[FRONT_MAX_ROWS];
+    const PlanParams& pp = fp.plan;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int T = pp.T, K = pp.top_k, El = pp.num_local;
+    const bool publish = blockIdx.x == 0;
+    const int n = T * K;
+
+    for (int i = tid; i < El; i += blockDim.x) s_cnt[i] = 0;
+    pdl_wait();
+    pdl_launch();
+    __syncthreads();
+
+    // ---- the routing result of all tokens, and the histogram of the local experts
+    for (int i = tid; i < n; i += blockDim.x) {
+        const int id = pp.topk_idx[i];
+        s_idx[i] = id;
+        s_w[i] = pp.topk_w[i];
+        const int le = id - pp.local_offset;
+        if (le >= 0 && le < El) atomicAdd(&s_cnt[le], 1);
+    }
+    __syncthreads();
+
+    // ---- scan
+    if (warp == 0) scan_counts(s_cnt, El, pp.token_tile, s_row0, s_tiles, publish ? pp.status : nullptr, lane);
+    __syncthreads();
+    const int total_rows = s_row0[El];
+    if (publish) {
+        for (int i = tid; i <= El; i += blockDim.x) {
+            pp.expert_row0[i] = s_row0[i];
+            pp.tile_prefix[i] = s_tiles[i];
+            if (i < El) pp.counts[i] = s_cnt[i];
+        }
+    }
+    for (int r = tid; r < total_rows; r += blockDim.x) s_row_token[r] = -1;
+    __syncthreads();
+
+    // ---- stable permutation: a warp places one expert's pairs in token order (ballot ranks)
+    for (int e = warp; e < El; e += FRONT_THREADS / 32) {
+        if (s_cnt[e] == 0) continue;
+        const int ge = e + pp.local_offset;
+        int placed = 0;
+        for (int base = 0; base < n; base += 32) {
+            const int i = base + lane;
+            const bool hit = i < n && s_idx[i] == ge;
+            const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
+            if (hit) {
+                const int r = s_row0[e] + placed + __popc(m & ((1u << lane) - 1u));
+                s_row_token[r] = i / K;
+                if (publish) { pp.pair_row[i] = r; pp.row_w[r] = s_w[i]; }
+            }
+            placed += __popc(m);
+        }
+    }
+    __syncthreads();
+    if (publish) {
+        for (int r = tid; r < total_rows; r += blockDim.x) {
+            const int t = s_row_token[r];
+            pp.row_token[r] = t;
+            if (t < 0) pp.row_w[r] = 0.f;
+        }
+    }
+
+    // ---- gather: one warp per row, rows dealt round-robin over all warps of the grid
+    const int H = fp.H, KB = H >> 7, rows_cap = pp.rows_cap;
+    for (int r = blockIdx.x * (FRONT_THREADS / 32) + warp; r < total_rows; r += gridDim.x * (FRONT_THREADS / 32)) {
+        const int t = s_row_token[r];
+        if (t < 0) continue;     // padding rows stay unwritten: their columns are never stored by the GEMMs
+        uint4* dst = reinterpret_cast<uint4*>(fp.a_perm + (size_t)r * H);
+        const uint4* src = reinterpret_cast<const uint4*>(fp.hidden + (size_t)t * H);
+        for (int i = lane; i < H / 16; i += 32) dst[i] = __ldg(src + i);
+        for (int kb = lane; kb < KB; kb += 32)
+            fp.a_scale_perm[(size_t)kb * rows_cap + r] = __ldg(fp.hscale + (size_t)kb * T + t);
+    }
+}
+
+}  // namespace b200moe

@@ -56,6 +56,7 @@ struct GemmParams {
     int evict_first_weights;
     int* sk_count;        // [2 * gridDim.x] arrival counters of split units (zero at launch)
     float* sk_partial;    // [2 * gridDim.x] slots of SLOT_FLOATS floats
+    long long* trace;     // [gridDim.x][TRACE_SLOTS]: slot 0 = %globaltimer at entry, others = SM clocks since entry
     int ablate;           // timing experiments only (results are wrong when non-zero): 1 = issue no MMA,
                           // 2 = promotion skips tcgen05.ld/FMA, 4 = producer skips the token-side loads
 };
@@ -104,6 +105,11 @@ struct GemmCfg {
 
 constexpr int SK_SLOT_FLOATS_MAX = 2 * 128 * 128;   // largest SLOT_FLOATS (GEMM1, 128 tokens)
 
+// Per-CTA time line (SM clock cycles since kernel entry) written by whichever thread reaches the point.
+enum : int { TR_ENTRY = 0, TR_PROLOGUE = 1, TR_TMA_FIRST = 2, TR_TMA_LAST = 3, TR_MMA_FIRST = 4, TR_MMA_LAST = 5,
+             TR_PROMO_FIRST = 6, TR_PROMO_LAST = 7, TR_PARTIAL = 8, TR_REDUCED = 9, TR_EPILOGUE = 10, TR_EXIT = 11,
+             TRACE_SLOTS = 16 };
+
 struct Unit { int e, mt, tt, row0, nvalid; };
 
 __device__ __forceinline__ bool decode_unit(int u, int n_mtiles, int num_local, int ntok, const int* s_tiles,
@@ -135,18 +141,15 @@ __device__ __forceinline__ int sk_owner(long long x, long long total, long long 
     return (int)c;
 }
 
-// Per-CTA work list: q whole units, then one contiguous range of the K-split tail.
+// Per-CTA work list: one contiguous range of the K-split units, then q whole units.
 struct SkSched { int NG, q, U0; long long total, grid, t_lo, t_hi; };
 struct SkSeg { int u, gb, ge; bool tail_first; };
 struct SkIter {
     int i; long long g;
     __device__ __forceinline__ void reset(const SkSched& s) { i = 0; g = s.t_lo; }
+    // The K-split range comes FIRST: its partial sums are published and added up while every CTA
+    // still has whole units to stream, so the fix-up latency is hidden behind useful traffic.
     __device__ __forceinline__ bool next(const SkSched& s, SkSeg& o) {
-        if (i < s.q) {
-            o.u = i * (int)gridDim.x + (int)blockIdx.x; o.gb = 0; o.ge = s.NG; o.tail_first = false;
-            ++i;
-            return true;
-        }
         if (g < s.t_hi) {
             const int ut = (int)(g / s.NG);
             o.gb = (int)(g - (long long)ut * s.NG);
@@ -154,6 +157,11 @@ struct SkIter {
             o.u = s.U0 + ut;
             o.tail_first = (g == s.t_lo);
             g += o.ge - o.gb;
+            return true;
+        }
+        if (i < s.q) {
+            o.u = i * (int)gridDim.x + (int)blockIdx.x; o.gb = 0; o.ge = s.NG; o.tail_first = false;
+            ++i;
             return true;
         }
         return false;
@@ -204,6 +212,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     int* s_flag = reinterpret_cast<int*>(s_red + C::NPW * C::NC);   // [2] arrival order of a split unit, per group
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long t_entry = clock64();
+    long long* const trace = p.trace ? p.trace + (size_t)blockIdx.x * TRACE_SLOTS : nullptr;
+    auto stamp = [&](int slot) { if (trace) trace[slot] = clock64() - t_entry; };
+    if (trace && threadIdx.x == 0) trace[TR_ENTRY] = (long long)globaltimer_ns();
     const uint32_t bar_full = smem_u32(bars);
     const uint32_t bar_empty = bar_full + 8 * C::STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * C::STAGES;
@@ -234,6 +246,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
     const uint32_t smem_base = smem_u32(smem);
+    if (threadIdx.x == 0) stamp(TR_PROLOGUE);
 
     // Schedule.  Units are numbered so that the token tiles of one (expert, row tile) are adjacent.
     // The first q*gridDim.x units run as whole units, round-robin (CTAs that run at the same time
@@ -263,7 +276,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         if (lane == 0) {
             const uint64_t pol = policy_evict_first();
             int stage = 0; uint32_t phase = 0;
-            bool ok = true;
+            bool ok = true, issued = false;
             SkIter it; it.reset(sc);
             SkSeg sg;
             while (ok && it.next(sc, sg)) {
@@ -291,9 +304,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         if (!G1) tma_load_2d(st + C::NA * C::A_BYTES + C::B_BYTES, &tm_b1, kb * 128, un.row0, full);
                         bulk_load(st + C::SC_OFF, p.b_scale + (size_t)kb * p.rows_cap + un.row0, NTOK * 4, full);
                     }
+                    if (!issued) { stamp(TR_TMA_FIRST); issued = true; }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
+            stamp(TR_TMA_LAST);
             if (!ok) {
                 // give copies that are still in flight time to land before the CTA's shared memory goes away
                 for (int i = 0; i < 64; ++i) __nanosleep(10000);
@@ -306,7 +321,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             constexpr uint32_t idesc = make_idesc_f8(128, NTOK);
             int stage = 0; uint32_t phase = 0;
             int ab = 0; uint32_t aphase = 0;
-            bool ok = true;
+            bool ok = true, seen = false;
             SkIter it; it.reset(sc);
             SkSeg sg;
             while (ok && it.next(sc, sg)) {
@@ -316,6 +331,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     const int nj = min(C::KPB, p.KB - grp * C::KPB);
                     for (int j = 0; j < nj; ++j) {
                         if (!mbar_wait(bar_full + 8 * stage, phase, p.status, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
+                        if (!seen) { stamp(TR_MMA_FIRST); seen = true; }
                         tc_fence_after();
                         const uint32_t st = smem_base + stage * C::STAGE_BYTES;
                         const uint32_t d = tmem_base + ab * C::BUFCOLS + j * C::CPB;
@@ -355,6 +371,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     if (++ab == C::NACC) { ab = 0; aphase ^= 1; }
                 }
             }
+            stamp(TR_MMA_LAST);
         }
         __syncwarp();
     }
@@ -372,7 +389,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         int stage = 0; uint32_t phase = 0;
         int ab = 0; uint32_t aphase = 0;
         uint32_t rphase = 0;
-        bool ok = true;
+        bool ok = true, seen = false;
         float acc[C::NACCUM][C::NC];
 
         // the 4 warps of one column group meet (bounded); false = gave up
@@ -438,6 +455,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     }
                 }
                 if (!mbar_wait(bar_tfull + 8 * ab, aphase, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+                if (ptid == 0 && !seen) { stamp(TR_PROMO_FIRST); seen = true; }
                 tc_fence_after();
                 const uint32_t tbuf = tmem_base + tlane + ab * C::BUFCOLS + c0;
 
@@ -514,6 +532,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 if (++ab == C::NACC) { ab = 0; aphase ^= 1; }
             }
             if (!ok) break;
+            if (ptid == 0) stamp(TR_PROMO_LAST);
 
             if (!(gb == 0 && ge == NG)) {
                 // ---- split unit: publish the partial, the last CTA to arrive adds them up in CTA order
@@ -532,22 +551,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 if (!group_sync()) { ok = false; break; }
                 const bool last = s_flag[grp_id] == (c_last - c_first);
                 if (!group_sync()) { ok = false; break; }          // s_flag may be rewritten by the next split unit
+                if (ptid == 0) stamp(TR_PARTIAL);
                 if (!last) continue;
                 __threadfence();
 #pragma unroll
                 for (int a = 0; a < C::NACCUM; ++a)
 #pragma unroll
                     for (int i = 0; i < C::NC; ++i) acc[a][i] = 0.f;
-                for (int c = c_first; c <= c_last; ++c) {
+                auto slot_of = [&](int c) -> const float* {
                     const bool c_first_seg = (int)(sk_start(c, total, grid) / NG) == u - sc.U0;
-                    const float* src = p.sk_partial + (size_t)(c * 2 + (c_first_seg ? 0 : 1)) * SK_SLOT_FLOATS_MAX;
+                    return p.sk_partial + (size_t)(c * 2 + (c_first_seg ? 0 : 1)) * SK_SLOT_FLOATS_MAX + ptid;
+                };
+                if constexpr (C::NACCUM * C::NC <= 32) {
+                    // narrow tiles: the next CTA's slot is in flight while this one is added (same fixed order)
+                    float nxt[C::NACCUM * C::NC];
+                    const float* src = slot_of(c_first);
 #pragma unroll
-                    for (int a = 0; a < C::NACCUM; ++a)
+                    for (int k = 0; k < C::NACCUM * C::NC; ++k) nxt[k] = __ldcg(src + (size_t)k * C::NPT);
+                    for (int c = c_first; c <= c_last; ++c) {
+                        float cur[C::NACCUM * C::NC];
 #pragma unroll
-                        for (int i = 0; i < C::NC; ++i) acc[a][i] += __ldcg(src + (size_t)(a * C::NC + i) * C::NPT + ptid);
+                        for (int k = 0; k < C::NACCUM * C::NC; ++k) cur[k] = nxt[k];
+                        if (c < c_last) {
+                            src = slot_of(c + 1);
+#pragma unroll
+                            for (int k = 0; k < C::NACCUM * C::NC; ++k) nxt[k] = __ldcg(src + (size_t)k * C::NPT);
+                        }
+#pragma unroll
+                        for (int a = 0; a < C::NACCUM; ++a)
+#pragma unroll
+                            for (int i = 0; i < C::NC; ++i) acc[a][i] += cur[a * C::NC + i];
+                    }
+                } else {
+                    for (int c = c_first; c <= c_last; ++c) {
+                        const float* src = slot_of(c);
+#pragma unroll
+                        for (int a = 0; a < C::NACCUM; ++a)
+#pragma unroll
+                            for (int i = 0; i < C::NC; ++i) acc[a][i] += __ldcg(src + (size_t)(a * C::NC + i) * C::NPT);
+                    }
                 }
             }
 
+            if (ptid == 0) stamp(TR_REDUCED);
             if (G1) {
                 // SwiGLU, then amax over the 128 rows of the tile for every token column
                 uint32_t* red = s_red + pw * C::NC;
@@ -605,9 +651,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         }
     }
 
+    if (warp >= 4 && threadIdx.x == 128) stamp(TR_EPILOGUE);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
+    if (threadIdx.x == 0) stamp(TR_EXIT);
 }
 
 }  // namespace b200moe

@@ -45,6 +45,52 @@ __global__ void count_kernel(const int32_t* __restrict__ topk_idx, int n, int lo
     }
 }
 
+// Warp-parallel exclusive scan over the (<= 256) per-expert counts: lane l owns experts
+// [l*per, (l+1)*per).  Fills s_row0[0..n] (first row of each expert, segments padded to
+// ROW_ALIGN) and s_tiles[0..n] (exclusive prefix of token tiles); writes the totals into
+// status[] when it is not null.  Must be called by the 32 lanes of one warp.
+__device__ __forceinline__ void scan_counts(const int* counts, int num_local, int token_tile, int* s_row0, int* s_tiles,
+                                            int* status, int tid) {
+    const int per = (num_local + 31) / 32;
+    int c[MAX_LOCAL / 32];
+    int rows = 0, tiles = 0, pairs = 0, active = 0;
+#pragma unroll
+    for (int k = 0; k < MAX_LOCAL / 32; ++k) {
+        const int i = tid * per + k;
+        c[k] = (k < per && i < num_local) ? counts[i] : 0;
+        rows += (c[k] + ROW_ALIGN - 1) / ROW_ALIGN * ROW_ALIGN;
+        tiles += (c[k] + token_tile - 1) / token_tile;
+        pairs += c[k]; active += c[k] > 0;
+    }
+    int rows_in = rows, tiles_in = tiles;
+    for (int off = 1; off < 32; off <<= 1) {
+        const int r = __shfl_up_sync(0xFFFFFFFFu, rows_in, off);
+        const int t = __shfl_up_sync(0xFFFFFFFFu, tiles_in, off);
+        if (tid >= off) { rows_in += r; tiles_in += t; }
+    }
+    for (int off = 16; off; off >>= 1) {
+        pairs += __shfl_xor_sync(0xFFFFFFFFu, pairs, off);
+        active += __shfl_xor_sync(0xFFFFFFFFu, active, off);
+    }
+    int r0 = rows_in - rows, t0 = tiles_in - tiles;       // exclusive prefixes of this lane
+#pragma unroll
+    for (int k = 0; k < MAX_LOCAL / 32; ++k) {
+        const int i = tid * per + k;
+        if (k < per && i < num_local) {
+            s_row0[i] = r0; s_tiles[i] = t0;
+            r0 += (c[k] + ROW_ALIGN - 1) / ROW_ALIGN * ROW_ALIGN;
+            t0 += (c[k] + token_tile - 1) / token_tile;
+        }
+    }
+    if (tid == 31) {
+        s_row0[num_local] = rows_in; s_tiles[num_local] = tiles_in;
+        if (status) {
+            status[ST_PAIRS] = pairs; status[ST_ROWS] = rows_in;
+            status[ST_TILES] = tiles_in; status[ST_ACTIVE] = active;
+        }
+    }
+}
+
 // One CTA per local expert.  Every CTA recomputes the (tiny) prefix over the counts, CTA 0
 // publishes it; then the CTA places its expert's pairs in token order.
 __global__ void __launch_bounds__(256) permute_kernel(const PlanParams p) {
@@ -55,45 +101,7 @@ __global__ void __launch_bounds__(256) permute_kernel(const PlanParams p) {
     pdl_wait();
     pdl_launch();
 
-    if (tid < 32) {
-        // warp-parallel exclusive scan over the (<= 256) counts: lane l owns experts [l*per, (l+1)*per)
-        const int per = (p.num_local + 31) / 32;
-        int c[MAX_LOCAL / 32];
-        int rows = 0, tiles = 0, pairs = 0, active = 0;
-#pragma unroll
-        for (int k = 0; k < MAX_LOCAL / 32; ++k) {
-            const int i = tid * per + k;
-            c[k] = (k < per && i < p.num_local) ? p.counts[i] : 0;
-            rows += (c[k] + ROW_ALIGN - 1) / ROW_ALIGN * ROW_ALIGN;
-            tiles += (c[k] + p.token_tile - 1) / p.token_tile;
-            pairs += c[k]; active += c[k] > 0;
-        }
-        int rows_in = rows, tiles_in = tiles;
-        for (int off = 1; off < 32; off <<= 1) {
-            const int r = __shfl_up_sync(0xFFFFFFFFu, rows_in, off);
-            const int t = __shfl_up_sync(0xFFFFFFFFu, tiles_in, off);
-            if (tid >= off) { rows_in += r; tiles_in += t; }
-        }
-        for (int off = 16; off; off >>= 1) {
-            pairs += __shfl_xor_sync(0xFFFFFFFFu, pairs, off);
-            active += __shfl_xor_sync(0xFFFFFFFFu, active, off);
-        }
-        int r0 = rows_in - rows, t0 = tiles_in - tiles;       // exclusive prefixes of this lane
-#pragma unroll
-        for (int k = 0; k < MAX_LOCAL / 32; ++k) {
-            const int i = tid * per + k;
-            if (k < per && i < p.num_local) {
-                s_row0[i] = r0; s_tiles[i] = t0;
-                r0 += (c[k] + ROW_ALIGN - 1) / ROW_ALIGN * ROW_ALIGN;
-                t0 += (c[k] + p.token_tile - 1) / p.token_tile;
-            }
-        }
-        if (tid == 31) { s_row0[p.num_local] = rows_in; s_tiles[p.num_local] = tiles_in; }
-        if (e == 0 && tid == 31) {
-            p.status[ST_PAIRS] = pairs; p.status[ST_ROWS] = rows_in;
-            p.status[ST_TILES] = tiles_in; p.status[ST_ACTIVE] = active;
-        }
-    }
+    if (tid < 32) scan_counts(p.counts, p.num_local, p.token_tile, s_row0, s_tiles, e == 0 ? p.status : nullptr, tid);
     __syncthreads();
     if (e == 0) {
         for (int i = tid; i <= p.num_local; i += blockDim.x) {
@@ -152,11 +160,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__
     for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
         const int t = row_token[r];
         uint4* dst = reinterpret_cast<uint4*>(a_perm + (size_t)r * H);
-        if (t < 0) {   // padding row: finite zeros so that no NaN pattern reaches the tensor core
-            for (int i = lane; i < H / 16; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
-            for (int kb = lane; kb < KB; kb += 32) a_scale_perm[(size_t)kb * rows_cap + r] = 0.f;
-            continue;
-        }
+        if (t < 0) continue;   // padding rows stay unwritten: their columns are never stored by the GEMMs
         const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * H);
         for (int i = lane; i < H / 16; i += 32) dst[i] = __ldg(src + i);
         for (int kb = lane; kb < KB; kb += 32) a_scale_perm[(size_t)kb * rows_cap + r] = __ldg(hscale + (size_t)kb * T + t);

@@ -33,13 +33,10 @@ __device__ __forceinline__ uint32_t ordered_key(float f) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// Routes token t with one warp.  On return lane r < top_k holds selection r: the global expert
+// id in sel_id and its weight in w.
 template <int VPT, int MODE>
-__global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
-    const int lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    pdl_wait();
-    pdl_launch();
-    if (t >= p.T) return;
+__device__ __forceinline__ void route_token(const RouteParams& p, int t, int lane, int& sel_id, float& w) {
     const unsigned FULL = 0xFFFFFFFFu;
 
     float s[VPT];   // value the weights are taken from (sigmoid / softmax probability)
@@ -99,7 +96,7 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) key[i] = kept ? ordered_key(v[i]) : 0u;  // 0 < every real key
 
-    int sel_id = -1;        // lane r < top_k ends up holding selection r
+    sel_id = -1;            // lane r < top_k ends up holding selection r
     float sel_s = 0.f;
     float ssum = 0.f;
     for (int r = 0; r < p.top_k; ++r) {
@@ -123,8 +120,19 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
         if (lane == r) { sel_id = win * VPT + wi; sel_s = ws; }
         ssum = __fadd_rn(ssum, ws);
     }
+    w = __fmul_rn(__fdiv_rn(sel_s, __fadd_rn(ssum, 1e-20f)), p.scale);
+}
+
+template <int VPT, int MODE>
+__global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_wait();
+    pdl_launch();
+    if (t >= p.T) return;
+    int sel_id; float w;
+    route_token<VPT, MODE>(p, t, lane, sel_id, w);
     if (lane < p.top_k) {
-        const float w = __fmul_rn(__fdiv_rn(sel_s, __fadd_rn(ssum, 1e-20f)), p.scale);
         p.topk_idx[(size_t)t * p.top_k + lane] = sel_id;
         p.topk_w[(size_t)t * p.top_k + lane] = w;
         const int le = sel_id - p.local_offset;

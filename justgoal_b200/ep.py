@@ -1,0 +1,129 @@
+"""Expert-parallel MoE layer: experts sharded over the ranks of one node, tokens sharded evenly.
+
+The reference corpus has no distributed code; its operator is ONE rank's share of a layer
+(`local_expert_offset`, 32 local of 256 experts: goal_full_shape/fable-5.1/moe_fp8_fwd/<def>/
+moe_common.cuh:14-15).  This module supplies the two exchanges around that share:
+
+  route own tokens -> DISPATCH (all-to-all of fp8 rows + scales + the token's top-k ids/weights,
+  one copy per (token, destination rank)) -> local experts (b200moe_forward_routed: fp32 sum over
+  the local experts of a received token) -> COMBINE (all-to-all of bf16 partial rows back to the
+  token's owner) -> fp32 sum over the destination ranks, one rounding to bf16.
+
+One process per GPU, `torch.distributed` (NCCL over NVLink) for the exchange.  The exchange logic
+is independent of where routing and the expert math run: `route_fn` / `experts_fn` default to the
+CUDA library and can be replaced (the CPU tests run the same exchange over gloo with the oracle
+as the local compute).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from .inputs import MoEShape
+
+
+@dataclass
+class DispatchPlan:
+    """Who gets which of my tokens.  `send_token[i]` is the local token of the i-th sent row; rows
+    are grouped by destination rank (ascending), tokens ascending inside a group."""
+    send_token: torch.Tensor        # int64 [n_send]
+    send_counts: list               # rows per destination rank
+    recv_counts: list               # rows per source rank
+
+
+def plan_dispatch(topk_idx: torch.Tensor, experts_per_rank: int, world: int, group=None) -> DispatchPlan:
+    """De-duplicated per (token, destination rank): a token with several experts on one rank is
+    sent there once."""
+    dst = torch.div(topk_idx.long(), experts_per_rank, rounding_mode="floor")          # [T, K]
+    T = topk_idx.shape[0]
+    mask = torch.zeros(T, world, dtype=torch.bool, device=topk_idx.device)
+    mask.scatter_(1, dst.clamp_(0, world - 1), True)
+    pairs = torch.nonzero(mask.t(), as_tuple=False)                                     # (rank, token), sorted
+    send_counts = torch.bincount(pairs[:, 0], minlength=world)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    both = torch.stack([send_counts, recv_counts]).cpu()                                # the one host sync of a step
+    return DispatchPlan(pairs[:, 1].contiguous(), both[0].tolist(), both[1].tolist())
+
+
+def _a2a(x: torch.Tensor, out_rows: int, in_splits, out_splits, group):
+    out = torch.empty((out_rows,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    if x.dtype == torch.float8_e4m3fn:      # NCCL moves bytes; view fp8 as uint8
+        dist.all_to_all_single(out.view(torch.uint8), x.view(torch.uint8), out_splits, in_splits, group=group)
+    else:
+        dist.all_to_all_single(out, x, out_splits, in_splits, group=group)
+    return out
+
+
+class ExpertParallelMoE:
+    def __init__(self, shape: MoEShape, weights: dict, group=None, route_fn=None, experts_fn=None, device=None):
+        """`shape.num_local_experts` experts per rank, rank r owning experts [r*E_local, (r+1)*E_local);
+        `weights` = this rank's gemm1/gemm2 weights and scales."""
+        self.shape, self.group, self.w = shape, group, weights
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if shape.num_local_experts * self.world != shape.num_experts:
+            raise ValueError("num_local_experts * world_size must equal num_experts")
+        self.offset = self.rank * shape.num_local_experts
+        self._layer = None
+        if route_fn is None or experts_fn is None:
+            from .main import MoELayer
+            self._layer = MoELayer(shape, device)
+        self.route_fn = route_fn or self._route_cuda
+        self.experts_fn = experts_fn or self._experts_cuda
+        self.last_plan = None
+
+    # ---- default local compute: the CUDA library
+    def _route_cuda(self, logits, bias, rsf):
+        return self._layer.route(logits, bias, rsf)
+
+    def _experts_cuda(self, idx, w, hidden, hscale):
+        return self._layer.forward_routed(idx, w, hidden, hscale, self.w["gemm1_weights"],
+                                          self.w["gemm1_weights_scale"], self.w["gemm2_weights"],
+                                          self.w["gemm2_weights_scale"], self.offset)
+
+    # ---- one step
+    @torch.no_grad()
+    def forward(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, routed_scaling_factor):
+        """Inputs are this rank's tokens (hidden_states_scale is [H/128, T_local]); returns bf16
+        [T_local, H], the full layer output for those tokens."""
+        s, g = self.shape, self.group
+        T, H = hidden_states.shape
+        idx, w = self.route_fn(routing_logits, routing_bias, routed_scaling_factor)
+        plan = plan_dispatch(idx, s.num_local_experts, self.world, g)
+        self.last_plan = plan
+        tok = plan.send_token
+        n_recv = sum(plan.recv_counts)
+        # DISPATCH: rows, scales (token-major on the wire), ids and weights of every sent token
+        x_send = hidden_states.view(torch.uint8).index_select(0, tok).view(torch.float8_e4m3fn)
+        sc_send = hidden_states_scale.t().index_select(0, tok).contiguous()
+        idx_send = idx.to(torch.int32).index_select(0, tok)
+        w_send = w.index_select(0, tok)
+        x_recv = _a2a(x_send, n_recv, plan.send_counts, plan.recv_counts, g)
+        sc_recv = _a2a(sc_send, n_recv, plan.send_counts, plan.recv_counts, g)
+        idx_recv = _a2a(idx_send, n_recv, plan.send_counts, plan.recv_counts, g)
+        w_recv = _a2a(w_send, n_recv, plan.send_counts, plan.recv_counts, g)
+        # LOCAL EXPERTS: fp32 sum over this rank's experts for every received token
+        if n_recv:
+            part = self.experts_fn(idx_recv, w_recv, x_recv, sc_recv.t().contiguous())
+        else:
+            part = torch.zeros(0, H, dtype=torch.float32, device=hidden_states.device)
+        # COMBINE: bf16 partial rows back to the owners, fp32 sum over destination ranks, one rounding
+        back = _a2a(part.to(torch.bfloat16), tok.numel(), plan.recv_counts, plan.send_counts, g)
+        out = torch.zeros(T, H, dtype=torch.float32, device=hidden_states.device)
+        out.index_add_(0, tok, back.float())
+        return out.to(torch.bfloat16)
+
+    def nvlink_bytes(self):
+        """Bytes this rank sent to OTHER ranks in the last step (dispatch + combine partials received
+        count on the peers' side): the figure the NVLink term of the roofline uses."""
+        p, s = self.last_plan, self.shape
+        if p is None:
+            return 0
+        remote_send = sum(c for d, c in enumerate(p.send_counts) if d != self.rank)
+        remote_recv = sum(c for d, c in enumerate(p.recv_counts) if d != self.rank)
+        row = s.hidden + 4 * (s.hidden // 128) + 8 * s.top_k
+        return {"dispatch_send": remote_send * row, "combine_send": remote_recv * 2 * s.hidden,
+                "dispatch_recv": remote_recv * row, "combine_recv": remote_send * 2 * s.hidden}
