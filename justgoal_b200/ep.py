@@ -127,3 +127,109 @@ class ExpertParallelMoE:
         row = s.hidden + 4 * (s.hidden // 128) + 8 * s.top_k
         return {"dispatch_send": remote_send * row, "combine_send": remote_recv * 2 * s.hidden,
                 "dispatch_recv": remote_recv * row, "combine_recv": remote_send * 2 * s.hidden}
+
+
+# ---------------------------------------------------------------------------------------------
+# benchmark leg for bench.py (N > 1)
+# ---------------------------------------------------------------------------------------------
+def bench(args, spec, name, rank, world, local):
+    """One step = one expert-parallel forward of the whole layer over T tokens (T/world per rank).
+    Timed with CUDA events between barriers; the step time is the maximum over ranks."""
+    import json
+    import time
+
+    from . import inputs as I
+
+    dev = torch.device("cuda", local)
+    shape, T = spec["shape"], spec["T"]
+    per = T // world
+    tokens = I.make_tokens(shape, T, seed=0, device=dev)
+    sl = slice(rank * per, (rank + 1) * per)
+    logits = tokens["routing_logits"][sl].contiguous()
+    bias = tokens["routing_bias"]
+    hidden = tokens["hidden_states"].view(torch.uint8)[sl].contiguous().view(torch.float8_e4m3fn)
+    hscale = tokens["hidden_states_scale"][:, sl].contiguous()
+    weights = I.make_weights(shape, 0, dev, rank * shape.num_local_experts)
+    ep = ExpertParallelMoE(shape, weights, device=dev)
+    K, W = args.steps, max(args.warmup, 3)
+
+    def sync_time(fn, steps):
+        for _ in range(W):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(); dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t)
+
+    out = None
+
+    def step():
+        nonlocal out
+        out = ep.forward(logits, bias, hidden, hscale, spec["rsf"])
+
+    ms_step = sync_time(step, K)
+    nv = ep.nvlink_bytes()
+
+    host_in = [t.cpu().pin_memory() for t in (logits, hidden, hscale)]
+    dev_in = [torch.empty_like(t) for t in (logits, hidden, hscale)]
+    host_out = torch.empty(per, shape.hidden, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        for src, dst in zip(host_in, dev_in):
+            dst.copy_(src, non_blocking=True)
+        o = ep.forward(dev_in[0], bias, dev_in[1], dev_in[2], spec["rsf"])
+        host_out.copy_(o, non_blocking=True)
+
+    e2e_ms = sync_time(e2e_step, K)
+    h2d = sum(t.numel() * t.element_size() for t in host_in) * world
+    d2h = host_out.numel() * host_out.element_size() * world
+
+    # realised work over all ranks
+    n_recv = torch.tensor([sum(ep.last_plan.recv_counts)], device=dev, dtype=torch.float64)
+    idx, _ = ep.route_fn(logits, bias, spec["rsf"])
+    pairs = torch.tensor([float(idx.numel())], device=dev, dtype=torch.float64)
+    link = torch.tensor([float(max(nv["dispatch_send"] + nv["combine_send"], nv["dispatch_recv"] + nv["combine_recv"]))],
+                        device=dev, dtype=torch.float64)
+    dist.all_reduce(pairs); dist.all_reduce(n_recv); dist.all_reduce(link, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        H, Iz = shape.hidden, shape.intermediate
+        flops = 6 * float(pairs) * H * Iz
+        w_bytes_rank = shape.num_local_experts * 3 * H * Iz
+        line = {
+            "metric": "moe_layer_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 (block-scaled), bf16 out", "data": "synthetic",
+            "config": {"workload": f"{name}: T={T} per step over {world} ranks, hidden {H}, intermediate {Iz}, "
+                                   f"{shape.num_local_experts} of {shape.num_experts} experts per rank, top-{shape.top_k}, "
+                                   "expert parallel (NCCL all-to-all dispatch/combine)",
+                       "l2": "inputs larger than L2 (%.2f GB of expert weights per rank)" % (w_bytes_rank / 1e9)},
+            "e2e": {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": int(ep._layer.launches_per_forward(per)) * K * world if ep._layer else 0,
+            "roofline": {"kernel": "whole step, slowest rank", "bound": "hbm", "peak_source": "measured",
+                         "achieved": w_bytes_rank / (ms_step * 1e-3) / 1e9, "peak": _hbm_peak(), "unit": "GB/s",
+                         "frac": w_bytes_rank / (ms_step * 1e-3) / 1e9 / _hbm_peak(), "traffic": None,
+                         "t_hbm_ms": w_bytes_rank / _hbm_peak() / 1e6, "t_fp8_ms": flops / world / 4.5e15 * 1e3,
+                         "t_nvlink_ms": float(link) / 770e9 * 1e3},
+            "layer": {"flops": flops, "tflops": flops / (ms_step * 1e-3) / 1e12, "pairs": float(pairs),
+                      "rows_dispatched": float(n_recv), "max_link_bytes_per_rank": float(link)},
+        }
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _hbm_peak():
+    import json
+    import os
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"])
+    except Exception:
+        return 6650.0

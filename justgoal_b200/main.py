@@ -56,13 +56,19 @@ class MoELayer:
 
     # ------------------------------------------------------------------ workspace
     def workspace(self, T: int) -> torch.Tensor:
-        ws = self._ws.get(T)
+        """Workspace for a forward over T tokens.  Buffers are cached per power-of-two bucket of T
+        (sizes grow monotonically with T, so the bucket's buffer serves every smaller count), which
+        keeps memory bounded when the token count changes from call to call."""
+        bucket = 64
+        while bucket < T:
+            bucket *= 2
+        ws = self._ws.get(bucket)
         if ws is None:
             n = C.c_size_t()
-            _lib.check(_lib.lib.b200moe_workspace_bytes(self._h, T, C.byref(n)), "b200moe_workspace_bytes")
+            _lib.check(_lib.lib.b200moe_workspace_bytes(self._h, bucket, C.byref(n)), "b200moe_workspace_bytes")
             ws = torch.empty(max(int(n.value), 256), dtype=torch.uint8, device=self.device)
             assert ws.data_ptr() % 256 == 0
-            self._ws[T] = ws
+            self._ws[bucket] = ws
         return ws
 
     def layout(self, T: int) -> _lib.WsLayout:
