@@ -68,7 +68,7 @@ typedef struct b200moe_ws_layout {
     size_t act_lo;        /* uint8[rows_cap, I] e4m3 of the rounding residual              */
     size_t act_scale;     /* float[I/128, rows_cap]                                        */
     size_t y;             /* float[rows_cap, H] weighted expert outputs per row            */
-    size_t sk_count;      /* int32[2][2*SMs] arrival counters of K-split units (GEMM1, GEMM2)*/
+    size_t sk_count;      /* int32[2][4*SMs] arrival counters of K-split units (GEMM1, GEMM2)*/
     size_t sk_partial;    /* float[2*SMs][32768] fp32 partial accumulators of K-split units */
     size_t trace;         /* int64[2][SMs][16] per-CTA time lines of GEMM1 and GEMM2: slot 0 =
                              %globaltimer at entry, slots 1..11 = SM clocks since entry at:

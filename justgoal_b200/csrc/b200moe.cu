@@ -131,7 +131,7 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, A); return o; };
     L->status = take(8 * 4);
     L->counts = take((size_t)El * 4);
-    L->sk_count = take((size_t)2 * 2 * h->num_sms * 4);       // [GEMM1 | GEMM2][2 * grid]; zeroed with the head
+    L->sk_count = take((size_t)2 * 4 * h->num_sms * 4);       // [GEMM1 | GEMM2][4 * grid]; zeroed with the head
     L->expert_row0 = take((size_t)(El + 1) * 4);
     L->tile_prefix = take((size_t)(El + 1) * 4);
     L->topk_idx = take((size_t)T * K * 4);
@@ -146,7 +146,7 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     L->act_scale = take((size_t)(c.intermediate / 128) * rows * 4);
     L->y = take(rows * c.hidden * 4);
     L->sk_partial = take((size_t)2 * h->num_sms * SK_SLOT_FLOATS_MAX * 4);
-    L->trace = take((size_t)2 * h->num_sms * TRACE_SLOTS * 8);   // [GEMM1 | GEMM2][CTA][slot]
+    L->trace = take((size_t)2 * h->num_sms * TRACE_SLOTS * 8 + 2 * 4 * KLOG_N * 8);   // [GEMM1 | GEMM2][CTA][slot], then K-block logs
     L->rows_cap = rows;
     L->token_tile = (size_t)pick_token_tile(c, T);
     L->total_bytes = off;
@@ -154,8 +154,15 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
 
 template <int NTOK, bool G1>
 cudaError_t set_attr() {
-    return cudaFuncSetAttribute(gemm_kernel<NTOK, G1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                GemmCfg<NTOK, G1>::SMEM_BYTES);
+    using C = GemmCfg<NTOK, G1>;
+    if (C::REALLOC_REGS) {
+        // the kernel's setmaxnreg arithmetic assumes the launch allocation; refuse to run otherwise
+        cudaFuncAttributes fa;
+        cudaError_t e = cudaFuncGetAttributes(&fa, gemm_kernel<NTOK, G1>);
+        if (e != cudaSuccess) return e;
+        if (fa.numRegs != C::LAUNCH_REGS) return cudaErrorInvalidConfiguration;
+    }
+    return cudaFuncSetAttribute(gemm_kernel<NTOK, G1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
 }
 
 template <int NTOK, bool G1>
@@ -271,7 +278,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
         CU_TRY(prof_mark(h, 2, st));
         CU_TRY(prof_mark(h, 3, st));
     } else {
-        CU_TRY(launch_k(PDL_PERMUTE, permute_kernel, dim3(El), dim3(256), 0, st, pp));
+        CU_TRY(launch_k(PDL_PERMUTE, permute_kernel, dim3(El), dim3(PERMUTE_THREADS), 0, st, pp));
         CU_TRY(prof_mark(h, 2, st));
 
         const long long max_rows = (long long)T * (c.top_k < El ? c.top_k : El) + (long long)ROW_ALIGN * El;
@@ -297,6 +304,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g1.sk_partial = reinterpret_cast<float*>(ws + L.sk_partial);
     g1.ablate = h->ablate & 0xFF;
     g1.trace = reinterpret_cast<long long*>(ws + L.trace);
+    g1.klog = g1.trace + (size_t)2 * h->num_sms * TRACE_SLOTS;
     CU_TRY(launch_gemm_ntok<true>(ntok, h->num_sms, st, m_w13, m_a, m_a, g1));
     CU_TRY(prof_mark(h, 4, st));
 
@@ -308,10 +316,11 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g2.w_scale = static_cast<const float*>(s2); g2.b_scale = act_scale; g2.rows_cap = rows_cap;
     g2.row_w = row_w; g2.y = y; g2.H = H; g2.I = I;
     g2.evict_first_weights = evf && ntok < 128;
-    g2.sk_count = reinterpret_cast<int*>(ws + L.sk_count) + 2 * h->num_sms;
+    g2.sk_count = reinterpret_cast<int*>(ws + L.sk_count) + 4 * h->num_sms;
     g2.sk_partial = g1.sk_partial;
     g2.ablate = (h->ablate >> 8) & 0xFF;
     g2.trace = g1.trace + (size_t)h->num_sms * TRACE_SLOTS;
+    g2.klog = g1.klog + 4 * KLOG_N;
     CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
     CU_TRY(prof_mark(h, 5, st));
 
@@ -548,7 +557,7 @@ int b200moe_permute_noalloc(b200moe_handle h, const int32_t* topk_idx, const flo
     pp.tile_prefix = reinterpret_cast<int*>(scratch + 1536);
     pp.pair_row = reinterpret_cast<int32_t*>(scratch + NOALLOC_HEAD_BYTES);
     pp.expert_row0 = expert_row0; pp.row_token = row_token; pp.row_w = row_w; pp.rows_cap = rows_capacity;
-    permute_kernel<<<El, 256, 0, st>>>(pp);
+    permute_kernel<<<El, PERMUTE_THREADS, 0, st>>>(pp);
     CU_TRY(cudaGetLastError());
     return 0;
 }

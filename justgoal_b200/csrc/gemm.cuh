@@ -29,6 +29,7 @@
 // warps 4.. = promotion/epilogue (4 or 8 warps; warp % 4 selects the TMEM lane quarter).
 // Every wait is bounded (common.cuh); no TMA load uses cluster multicast.
 #pragma once
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include "common.cuh"
 #include "permute.cuh"
@@ -54,8 +55,10 @@ struct GemmParams {
     uint8_t* act_hi; uint8_t* act_lo; float* act_scale; int I;   // GEMM1 outputs
     const float* row_w; float* y; int H;                          // GEMM2 outputs
     int evict_first_weights;
-    int* sk_count;        // [2 * gridDim.x] arrival counters of split units (zero at launch)
+    int* sk_count;        // [4 * gridDim.x] arrival counters of split units (zero at launch)
     float* sk_partial;    // [2 * gridDim.x] slots of SLOT_FLOATS floats
+    long long* klog;      // [4][KLOG_N]: CTA 0's clock at its first KLOG_N K blocks: TMA issue, data seen by the
+                          // MMA warp, group seen by the promotion warps, group folded (hand-back)
     long long* trace;     // [gridDim.x][TRACE_SLOTS]: slot 0 = %globaltimer at entry, others = SM clocks since entry
     int ablate;           // timing experiments only (results are wrong when non-zero): 1 = issue no MMA,
                           // 2 = promotion skips tcgen05.ld/FMA, 4 = producer skips the token-side loads
@@ -82,24 +85,38 @@ struct GemmCfg {
     static constexpr int BUFCOLS = KPB * CPB;               // TMEM columns per hand-off buffer
     static constexpr int NACC = (512 / BUFCOLS) > 4 ? 4 : (512 / BUFCOLS);
     static constexpr int TMEM_COLS = NACC * BUFCOLS;
-    static constexpr int NPW = NTOK >= 64 ? 8 : 4;         // promotion warps
+    // promotion warps.  Measured: the fold of a 128 x 256 fp32 block takes ~1.1 us however the
+    // tcgen05.ld are chunked, batched or spread over 8 or 16 warps - it is bound by the TMEM read
+    // rate (~128 KB per K block), not by instruction issue or load latency.
+    static constexpr int NPW = NTOK >= 64 ? 8 : 4;
+    static constexpr int NGRP = NPW / 4;                   // column groups (a group = 4 warps = all 128 lanes)
     static constexpr int NPT = 32 * NPW;                   // promotion threads
     static constexpr int NC = NTOK / (NPW / 4);            // token columns per promotion thread
     static constexpr int CH = (NACCUM * NC > 64) ? 16 : (NC < 32 ? NC : 32);   // columns per tcgen05.ld
     static constexpr int NTHREADS = 128 + NPT;
-    static constexpr bool REALLOC_REGS = NPW == 8;
+    // Register re-allocation (setmaxnreg).  The increase BLOCKS until the CTA's own pool holds enough
+    // registers, and that pool is only what the control warps gave back from the allocation the CTA
+    // was launched with - so the numbers below must add up exactly (checked here and, against the
+    // register count ptxas actually chose, by the host before the first launch).
+    static constexpr bool REALLOC_REGS = NPW >= 8;
+    static constexpr int LAUNCH_REGS = (65536 / NTHREADS) / 8 * 8;          // what __launch_bounds__(NTHREADS, 1) yields
+    static constexpr int CTRL_REGS = NPW == 16 ? 32 : 56;
+    static constexpr int PROMO_REGS = NPW == 16 ? 112 : 224;
+    static_assert(!REALLOC_REGS || 128 * CTRL_REGS + NPT * PROMO_REGS <= NTHREADS * LAUNCH_REGS,
+                  "setmaxnreg.inc would wait forever: the control warps do not release enough registers");
+    static_assert(!REALLOC_REGS || (CTRL_REGS <= LAUNCH_REGS && PROMO_REGS >= LAUNCH_REGS), "setmaxnreg direction");
     // narrow tiles: the promotion warps copy a group's token scales into registers as soon as the
     // stage has landed and release the stage at once, instead of holding it until the group is folded
-    static constexpr bool EARLY_SCALES = KPB * NC <= 32;
+    static constexpr bool EARLY_SCALES = KPB * NC <= 32 && NPW < 16;
     static constexpr int SLOT_FLOATS = NACCUM * NC * NPT;  // = NACCUM * 128 * NTOK
     static constexpr int TABLE_INTS = 3 * (MAX_LOCAL + 1);
     static constexpr int RED_BYTES = NPW * NC * 4;
     static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * STAGE_BYTES + 256 /*barriers*/ +
-                                      TABLE_INTS * 4 + RED_BYTES + 16;
+                                      TABLE_INTS * 4 + RED_BYTES + 32;
     static_assert(NTOK % 16 == 0 && NTOK >= 16 && NTOK <= 128, "token tile");
     static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "tmem");
     static_assert(STAGES >= KPB + 1, "a group must fit the stage ring with room to prefetch");
-    static_assert(NC % CH == 0 && (CH == 16 || CH == 32), "chunking");
+    static_assert(NC % CH == 0 && (CH == 8 || CH == 16 || CH == 32), "chunking");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
 
@@ -108,7 +125,7 @@ constexpr int SK_SLOT_FLOATS_MAX = 2 * 128 * 128;   // largest SLOT_FLOATS (GEMM
 // Per-CTA time line (SM clock cycles since kernel entry) written by whichever thread reaches the point.
 enum : int { TR_ENTRY = 0, TR_PROLOGUE = 1, TR_TMA_FIRST = 2, TR_TMA_LAST = 3, TR_MMA_FIRST = 4, TR_MMA_LAST = 5,
              TR_PROMO_FIRST = 6, TR_PROMO_LAST = 7, TR_PARTIAL = 8, TR_REDUCED = 9, TR_EPILOGUE = 10, TR_EXIT = 11,
-             TRACE_SLOTS = 16 };
+             TRACE_SLOTS = 16, KLOG_N = 64 };
 
 struct Unit { int e, mt, tt, row0, nvalid; };
 
@@ -173,7 +190,12 @@ __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + _
 template <int N>
 __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, float* v) {
     uint32_t r[N];
-    if constexpr (N == 16) {
+    if constexpr (N == 8) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+            : "r"(taddr) : "memory");
+    } else if constexpr (N == 16) {
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
             "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -209,24 +231,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     int* s_row0 = s_tiles + (MAX_LOCAL + 1);
     int* s_cnt = s_row0 + (MAX_LOCAL + 1);
     uint32_t* s_red = reinterpret_cast<uint32_t*>(s_cnt + (MAX_LOCAL + 1));
-    int* s_flag = reinterpret_cast<int*>(s_red + C::NPW * C::NC);   // [2] arrival order of a split unit, per group
+    int* s_flag = reinterpret_cast<int*>(s_red + C::NPW * C::NC);   // [NGRP] arrival order of a split unit, per group
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long t_entry = clock64();
     long long* const trace = p.trace ? p.trace + (size_t)blockIdx.x * TRACE_SLOTS : nullptr;
     auto stamp = [&](int slot) { if (trace) trace[slot] = clock64() - t_entry; };
+    long long* const klog = (p.klog && blockIdx.x == 0) ? p.klog : nullptr;
+    auto klog_put = [&](int row, int n) { if (klog && n < KLOG_N) klog[row * KLOG_N + n] = clock64() - t_entry; };
     if (trace && threadIdx.x == 0) trace[TR_ENTRY] = (long long)globaltimer_ns();
     const uint32_t bar_full = smem_u32(bars);
     const uint32_t bar_empty = bar_full + 8 * C::STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * C::STAGES;
     const uint32_t bar_tempty = bar_tfull + 8 * C::NACC;
     const uint32_t bar_red = bar_tempty + 8 * C::NACC;    // one per column group: its 4 warps meet here (bounded)
-    static_assert(8 * (2 * C::STAGES + 2 * C::NACC + 2) <= 240, "barrier area");
+    static_assert(8 * (2 * C::STAGES + 2 * C::NACC + 4) <= 240, "barrier area");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1 + C::NPW); }
         for (int b = 0; b < C::NACC; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, C::NPW); }
-        mbar_init(bar_red, 4); mbar_init(bar_red + 8, 4);
+        for (int g = 0; g < 4; ++g) mbar_init(bar_red + 8 * g, 4);
         mbar_fence_init();
         tma_prefetch_desc(&tm_w); tma_prefetch_desc(&tm_b0);
         if (!G1) tma_prefetch_desc(&tm_b1);
@@ -270,13 +294,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 
     if (warp < 4) {
     // ================================================================ control warpgroup
-    if (C::REALLOC_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (C::REALLOC_REGS) {
+        if (C::CTRL_REGS == 32) asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
+        else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    }
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             const uint64_t pol = policy_evict_first();
             int stage = 0; uint32_t phase = 0;
             bool ok = true, issued = false;
+            int nk = 0;
             SkIter it; it.reset(sc);
             SkSeg sg;
             while (ok && it.next(sc, sg)) {
@@ -305,6 +333,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         bulk_load(st + C::SC_OFF, p.b_scale + (size_t)kb * p.rows_cap + un.row0, NTOK * 4, full);
                     }
                     if (!issued) { stamp(TR_TMA_FIRST); issued = true; }
+                    klog_put(0, nk++);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -322,16 +351,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             int stage = 0; uint32_t phase = 0;
             int ab = 0; uint32_t aphase = 0;
             bool ok = true, seen = false;
+            int nk = 0;
             SkIter it; it.reset(sc);
             SkSeg sg;
             while (ok && it.next(sc, sg)) {
                 const int gb = sg.gb, ge = sg.ge;
+                if (p.ablate & 8) {      // timing experiment: consume stages directly, no MMA, no TMEM hand-off
+                    const int kb_end = min(p.KB, ge * C::KPB);
+                    for (int kb = gb * C::KPB; kb < kb_end && ok; ++kb) {
+                        if (!mbar_wait(bar_full + 8 * stage, phase, p.status, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
+                        for (int i = 0; i < 1 + C::NPW; ++i) mbar_arrive(bar_empty + 8 * stage);
+                        if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                    }
+                    continue;
+                }
                 for (int grp = gb; grp < ge && ok; ++grp) {
                     if (!mbar_wait(bar_tempty + 8 * ab, aphase ^ 1, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
                     const int nj = min(C::KPB, p.KB - grp * C::KPB);
                     for (int j = 0; j < nj; ++j) {
                         if (!mbar_wait(bar_full + 8 * stage, phase, p.status, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
                         if (!seen) { stamp(TR_MMA_FIRST); seen = true; }
+                        klog_put(1, nk++);
                         tc_fence_after();
                         const uint32_t st = smem_base + stage * C::STAGE_BYTES;
                         const uint32_t d = tmem_base + ab * C::BUFCOLS + j * C::CPB;
@@ -377,7 +417,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     }
     } else {
         // ------------------------------------------------------------ promotion + epilogue
-        if (C::REALLOC_REGS) asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        if (C::REALLOC_REGS) {
+            if (C::PROMO_REGS == 112) asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+            else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        }
         const int pw = warp - 4;
         const int quarter = warp & 3;                  // TMEM lanes [32*quarter, +32)
         const int grp_id = pw >> 2;                    // column group (0 when NPW == 4)
@@ -390,6 +433,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         int ab = 0; uint32_t aphase = 0;
         uint32_t rphase = 0;
         bool ok = true, seen = false;
+        int ng = 0;
         float acc[C::NACCUM][C::NC];
 
         // the 4 warps of one column group meet (bounded); false = gave up
@@ -403,7 +447,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 
         SkIter it; it.reset(sc);
         SkSeg sg;
-        while (ok && it.next(sc, sg)) {
+        while (ok && !(p.ablate & 8) && it.next(sc, sg)) {
             const int u = sg.u, gb = sg.gb, ge = sg.ge;
             const bool first_seg = sg.tail_first;
             Unit un;
@@ -418,15 +462,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             const float* ws0 = p.w_scale + ((size_t)un.e * p.scale_rows + srow0) * p.KB;
             const float* ws1 = p.w_scale + ((size_t)un.e * p.scale_rows + srow1) * p.KB;
 
+            // weight scales of a group are fetched one group ahead, so their global-load latency
+            // never sits between the TMEM hand-off and the first FMA
+            float swn[C::KPB][C::NACCUM];
+#pragma unroll
+            for (int j = 0; j < C::KPB; ++j) {
+                const int kb = min(gb * C::KPB + j, p.KB - 1);
+                swn[j][0] = __ldg(ws0 + kb);
+                swn[j][1] = __ldg(ws1 + kb);
+            }
             for (int grp = gb; grp < ge; ++grp) {
                 const int kb0 = grp * C::KPB;
                 const int nj = min(C::KPB, p.KB - kb0);
                 float sw[C::KPB][C::NACCUM];
 #pragma unroll
                 for (int j = 0; j < C::KPB; ++j) {
-                    const int kb = min(kb0 + j, p.KB - 1);
-                    sw[j][0] = __ldg(ws0 + kb);
-                    sw[j][1] = __ldg(ws1 + kb);
+                    sw[j][0] = swn[j][0]; sw[j][1] = swn[j][1];
+                    const int kb = min(kb0 + C::KPB + j, p.KB - 1);
+                    swn[j][0] = __ldg(ws0 + kb);
+                    swn[j][1] = __ldg(ws1 + kb);
                 }
                 const int st0 = stage;
                 float scr[C::EARLY_SCALES ? C::KPB : 1][C::EARLY_SCALES ? C::NC : 1];
@@ -456,6 +510,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 }
                 if (!mbar_wait(bar_tfull + 8 * ab, aphase, p.status, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
                 if (ptid == 0 && !seen) { stamp(TR_PROMO_FIRST); seen = true; }
+                if (ptid == 0) klog_put(2, ng);
                 tc_fence_after();
                 const uint32_t tbuf = tmem_base + tlane + ab * C::BUFCOLS + c0;
 
@@ -527,6 +582,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         }
                     }
                 }
+                if (ptid == 0) klog_put(3, ng++);
                 stage += nj;
                 if (stage >= C::STAGES) { stage -= C::STAGES; phase ^= 1; }
                 if (++ab == C::NACC) { ab = 0; aphase ^= 1; }
@@ -546,7 +602,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 __threadfence();
                 if (!group_sync()) { ok = false; break; }
                 if (quarter == 0 && lane == 0) {
-                    s_flag[grp_id] = atomicAdd(p.sk_count + c_first * 2 + grp_id, 1);
+                    s_flag[grp_id] = atomicAdd(p.sk_count + c_first * 4 + grp_id, 1);
                 }
                 if (!group_sync()) { ok = false; break; }
                 const bool last = s_flag[grp_id] == (c_last - c_first);
