@@ -112,3 +112,32 @@ def test_nonzero_expert_offset_matches_shifted_weights(ds_weights):
     r = util.run_oracle(shape, _cpu(d))
     rep = O.compare_output(out, r.output, util.ATOL, util.RTOL)
     assert rep["fail_frac"] == 0.0, rep
+
+
+def _share_check(shape, T, offset, rsf, seed):
+    """One rank's share of an expert-parallel configuration (its local experts, all T tokens)."""
+    from justgoal_b200 import MoELayer
+    d = I.make_tokens(shape, T, seed, "cuda")
+    d.update(I.make_weights(shape, seed, "cuda", offset))
+    d["local_expert_offset"] = offset
+    d["routed_scaling_factor"] = rsf
+    layer = MoELayer(shape)
+    out = layer.forward(*util.op_args(d))
+    torch.cuda.synchronize()
+    assert layer.status(T) == 0
+    r = util.run_oracle(shape, _cpu(d))
+    idx = layer.view(T, "topk_idx", torch.int32, (T, shape.top_k)).cpu()
+    assert bool(O.routing_sets_equal(idx, r.topk_idx).all())
+    rep = O.compare_output(out, r.output, util.ATOL, util.RTOL)
+    assert rep["finite"] and rep["fail_frac"] == 0.0, rep
+
+
+def test_ep_share_deepseek_128_local_experts():
+    """The 2-GPU expert-parallel share of the 256-expert layer: 128 local experts, second rank."""
+    _share_check(I.DEEPSEEK_V3.with_local(128), 512, 128, 2.5, seed=21)
+
+
+def test_ep_share_qwen3_shape():
+    """Qwen3-MoE shape (hidden 4096, intermediate 1536, 128 experts, 16 per rank, softmax top-8,
+    renormalised, no groups), one rank's share of the 8-GPU configuration at its full T=2048."""
+    _share_check(I.QWEN3_MOE, 2048, 48, 1.0, seed=22)
