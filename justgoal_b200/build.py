@@ -37,6 +37,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
     cmd = [_nvcc(), "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
            "-shared", "-Xcompiler", "-fPIC",
            "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
+    extra = os.environ.get("B200MOE_NVCC_FLAGS")      # e.g. -DB200MOE_ENABLE_ABLATE for timing experiments
+    if extra:
+        cmd[1:1] = extra.split()
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

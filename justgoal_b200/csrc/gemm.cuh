@@ -234,6 +234,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     int* s_flag = reinterpret_cast<int*>(s_red + C::NPW * C::NC);   // [NGRP] arrival order of a split unit, per group
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef B200MOE_ENABLE_ABLATE
+    const int kAblate = p.ablate;      // timing experiments (build with -DB200MOE_ENABLE_ABLATE)
+#else
+    constexpr int kAblate = 0;         // the ablation branches compile away in the product build
+#endif
     const long long t_entry = clock64();
     long long* const trace = p.trace ? p.trace + (size_t)blockIdx.x * TRACE_SLOTS : nullptr;
     auto stamp = [&](int slot) { if (trace) trace[slot] = clock64() - t_entry; };
@@ -319,7 +324,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, p.status, ERR_WAIT_SMEM_EMPTY)) { ok = false; break; }
                     const uint32_t st = smem_base + stage * C::STAGE_BYTES;
                     const uint32_t full = bar_full + 8 * stage;
-                    mbar_arrive_expect_tx(full, (p.ablate & 4) ? C::NA * C::A_BYTES : C::TX_BYTES);
+                    mbar_arrive_expect_tx(full, (kAblate & 4) ? C::NA * C::A_BYTES : C::TX_BYTES);
                     if (p.evict_first_weights) {
                         tma_load_2d_hint(st, &tm_w, kb * 128, wrow, full, pol);
                         tma_load_2d_hint(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full, pol);
@@ -327,7 +332,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         tma_load_2d(st, &tm_w, kb * 128, wrow, full);
                         tma_load_2d(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full);
                     }
-                    if (!(p.ablate & 4)) {
+                    if (!(kAblate & 4)) {
                         tma_load_2d(st + C::NA * C::A_BYTES, &tm_b0, kb * 128, un.row0, full);
                         if (!G1) tma_load_2d(st + C::NA * C::A_BYTES + C::B_BYTES, &tm_b1, kb * 128, un.row0, full);
                         bulk_load(st + C::SC_OFF, p.b_scale + (size_t)kb * p.rows_cap + un.row0, NTOK * 4, full);
@@ -356,7 +361,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             SkSeg sg;
             while (ok && it.next(sc, sg)) {
                 const int gb = sg.gb, ge = sg.ge;
-                if (p.ablate & 8) {      // timing experiment: consume stages directly, no MMA, no TMEM hand-off
+                if (kAblate & 8) {      // timing experiment: consume stages directly, no MMA, no TMEM hand-off
                     const int kb_end = min(p.KB, ge * C::KPB);
                     for (int kb = gb * C::KPB; kb < kb_end && ok; ++kb) {
                         if (!mbar_wait(bar_full + 8 * stage, phase, p.status, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
@@ -375,7 +380,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         tc_fence_after();
                         const uint32_t st = smem_base + stage * C::STAGE_BYTES;
                         const uint32_t d = tmem_base + ab * C::BUFCOLS + j * C::CPB;
-                        if (p.ablate & 1) {
+                        if (kAblate & 1) {
                         } else if (G1) {
                             const uint64_t a_up = make_smem_desc(st);
                             const uint64_t a_gate = make_smem_desc(st + C::A_BYTES);
@@ -447,7 +452,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 
         SkIter it; it.reset(sc);
         SkSeg sg;
-        while (ok && !(p.ablate & 8) && it.next(sc, sg)) {
+        while (ok && !(kAblate & 8) && it.next(sc, sg)) {
             const int u = sg.u, gb = sg.gb, ge = sg.ge;
             const bool first_seg = sg.tail_first;
             Unit un;
@@ -484,7 +489,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 }
                 const int st0 = stage;
                 float scr[C::EARLY_SCALES ? C::KPB : 1][C::EARLY_SCALES ? C::NC : 1];
-                if (C::EARLY_SCALES && !(p.ablate & 2)) {
+                if (C::EARLY_SCALES && !(kAblate & 2)) {
 #pragma unroll
                     for (int j = 0; j < C::KPB; ++j) {
                         if (j < nj) {
@@ -519,14 +524,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 constexpr int NCH = C::NC / C::CH;
                 constexpr int NK = C::KPB * NCH * C::NACCUM * C::NSPLIT;
                 float part[2][C::CH];
-                if (!(p.ablate & 2)) tmem_ld_chunk<C::CH>(tbuf, part[0]);
+                if (!(kAblate & 2)) tmem_ld_chunk<C::CH>(tbuf, part[0]);
 #pragma unroll
                 for (int k = 0; k < NK; ++k) {
                     const int sp = k % C::NSPLIT;
                     const int a = (k / C::NSPLIT) % C::NACCUM;
                     const int ch = (k / (C::NSPLIT * C::NACCUM)) % NCH;
                     const int j = k / (C::NSPLIT * C::NACCUM * NCH);
-                    if (j < nj && !(p.ablate & 2)) {
+                    if (j < nj && !(kAblate & 2)) {
                         tmem_wait_ld();
                         if (k + 1 < NK) {
                             const int sp1 = (k + 1) % C::NSPLIT;
@@ -575,7 +580,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(bar_tempty + 8 * ab);
-                    if (!C::EARLY_SCALES || (p.ablate & 2)) {
+                    if (!C::EARLY_SCALES || (kAblate & 2)) {
                         for (int j = 0; j < nj; ++j) {
                             int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
                             mbar_arrive(bar_empty + 8 * sj);
