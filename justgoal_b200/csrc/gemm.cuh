@@ -242,8 +242,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     const long long t_entry = clock64();
     long long* const trace = p.trace ? p.trace + (size_t)blockIdx.x * TRACE_SLOTS : nullptr;
     auto stamp = [&](int slot) { if (trace) trace[slot] = clock64() - t_entry; };
+#ifdef B200MOE_ENABLE_KLOG
     long long* const klog = (p.klog && blockIdx.x == 0) ? p.klog : nullptr;
     auto klog_put = [&](int row, int n) { if (klog && n < KLOG_N) klog[row * KLOG_N + n] = clock64() - t_entry; };
+#else
+    auto klog_put = [&](int, int) {};      // the per-K-block log is a build option (-DB200MOE_ENABLE_KLOG)
+#endif
     if (trace && threadIdx.x == 0) trace[TR_ENTRY] = (long long)globaltimer_ns();
     const uint32_t bar_full = smem_u32(bars);
     const uint32_t bar_empty = bar_full + 8 * C::STAGES;
