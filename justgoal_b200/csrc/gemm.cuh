@@ -100,8 +100,8 @@ struct GemmCfg {
     // register count ptxas actually chose, by the host before the first launch).
     static constexpr bool REALLOC_REGS = NPW >= 8;
     static constexpr int LAUNCH_REGS = (65536 / NTHREADS) / 8 * 8;          // what __launch_bounds__(NTHREADS, 1) yields
-    static constexpr int CTRL_REGS = NPW == 16 ? 32 : 56;
-    static constexpr int PROMO_REGS = NPW == 16 ? 112 : 224;
+    static constexpr int CTRL_REGS = NPW == 16 ? 32 : 40;
+    static constexpr int PROMO_REGS = NPW == 16 ? 112 : 232;
     static_assert(!REALLOC_REGS || 128 * CTRL_REGS + NPT * PROMO_REGS <= NTHREADS * LAUNCH_REGS,
                   "setmaxnreg.inc would wait forever: the control warps do not release enough registers");
     static_assert(!REALLOC_REGS || (CTRL_REGS <= LAUNCH_REGS && PROMO_REGS >= LAUNCH_REGS), "setmaxnreg direction");
@@ -305,7 +305,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     // ================================================================ control warpgroup
     if (C::REALLOC_REGS) {
         if (C::CTRL_REGS == 32) asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
-        else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        else asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
     }
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -428,7 +428,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         // ------------------------------------------------------------ promotion + epilogue
         if (C::REALLOC_REGS) {
             if (C::PROMO_REGS == 112) asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
-            else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+            else asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
         }
         const int pw = warp - 4;
         const int quarter = warp & 3;                  // TMEM lanes [32*quarter, +32)
