@@ -6,6 +6,7 @@
 Workloads (synthetic tensors with the benchmark definition's shapes and distributions):
   decode   T=64,   32 local of 256 experts, DeepSeek-V3 shape   (default at N=1; HBM-bound)
   prefill  T=4096, 32 local experts, 4 experts with ~4x the mean load
+  t14107   T=14107, 32 local experts (the shape the reference quotes its best latency on)
   ep       T=8192 per step, 256 experts sharded over the N ranks  (default at N>1)
   qwen3    T=2048, 128 experts of the Qwen3-MoE shape sharded over the N ranks
 
@@ -97,6 +98,8 @@ def workload_spec(name, n_gpus):
         return dict(shape=I.DEEPSEEK_V3, T=64, boost=None, ep=False, rsf=2.5)
     if name == "prefill":
         return dict(shape=I.DEEPSEEK_V3, T=4096, boost=((0, 8, 16, 24), PREFILL_BIAS_BOOST), ep=False, rsf=2.5)
+    if name == "t14107":      # the token count the reference quotes its best layer latency on (942 us)
+        return dict(shape=I.DEEPSEEK_V3, T=14107, boost=None, ep=False, rsf=2.5)
     if name == "ep":
         return dict(shape=I.DEEPSEEK_V3.with_local(256 // n_gpus), T=8192, boost=None, ep=True, rsf=2.5)
     if name == "qwen3":
@@ -330,7 +333,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=None, choices=[None, "decode", "prefill", "ep", "qwen3"])
+    ap.add_argument("--workload", default=None, choices=[None, "decode", "prefill", "t14107", "ep", "qwen3"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--cpu-budget", type=float, default=20.0)
     args = ap.parse_args()

@@ -76,6 +76,11 @@ struct GemmCfg {
     static constexpr int STAGES_RAW = (208 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int NACCUM = 2;                      // one accumulator per weight tile
+    // Orientation.  Narrow tiles put the weights on the MMA's M side (few tokens = few TMEM columns).
+    // A full 128-token tile puts the TOKENS on M (TMEM lanes) and each weight tile's 128 rows on N:
+    // a promotion thread then owns one token row, its scale is one scalar per K block (no per-column
+    // scale loads or multiplies in the fold) and it stores 64 contiguous output columns as vectors.
+    static constexpr bool TOK_ON_M = NTOK == 128;
     // Dependent MMAs into one accumulator serialise on the tensor pipe's latency, which dominates
     // for narrow token tiles; the MMAs of one K block are therefore spread over NSPLIT independent
     // partial accumulators (GEMM1: even/odd K step; GEMM2: hi / lo operand) that the promotion adds.
@@ -254,12 +259,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     const uint32_t bar_tfull = bar_empty + 8 * C::STAGES;
     const uint32_t bar_tempty = bar_tfull + 8 * C::NACC;
     const uint32_t bar_red = bar_tempty + 8 * C::NACC;    // one per column group: its 4 warps meet here (bounded)
-    static_assert(8 * (2 * C::STAGES + 2 * C::NACC + 4) <= 240, "barrier area");
+    const uint32_t bar_all = bar_red + 8 * 4;             // all promotion warps meet here (tokens-on-M epilogue)
+    static_assert(8 * (2 * C::STAGES + 2 * C::NACC + 5) <= 240, "barrier area");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1 + C::NPW); }
         for (int b = 0; b < C::NACC; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, C::NPW); }
         for (int g = 0; g < 4; ++g) mbar_init(bar_red + 8 * g, 4);
+        mbar_init(bar_all, C::NPW);
         mbar_fence_init();
         tma_prefetch_desc(&tm_w); tma_prefetch_desc(&tm_b0);
         if (!G1) tma_prefetch_desc(&tm_b1);
@@ -384,6 +391,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         tc_fence_after();
                         const uint32_t st = smem_base + stage * C::STAGE_BYTES;
                         const uint32_t d = tmem_base + ab * C::BUFCOLS + j * C::CPB;
+                        // mm(D, weight tile, token tile): operand order follows the orientation
+                        auto mm = [&](uint32_t dd, uint64_t wdesc, uint64_t tdesc, uint32_t accum) {
+                            if (C::TOK_ON_M) umma_f8(dd, tdesc, wdesc, idesc, accum);
+                            else umma_f8(dd, wdesc, tdesc, idesc, accum);
+                        };
                         if (kAblate & 1) {
                         } else if (G1) {
                             const uint64_t a_up = make_smem_desc(st);
@@ -392,8 +404,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {
                                 const int sp = k % C::NSPLIT;
-                                umma_f8(d + sp * NTOK, a_up + 2 * k, b + 2 * k, idesc, k >= C::NSPLIT);
-                                umma_f8(d + (C::NSPLIT + sp) * NTOK, a_gate + 2 * k, b + 2 * k, idesc, k >= C::NSPLIT);
+                                mm(d + sp * NTOK, a_up + 2 * k, b + 2 * k, k >= C::NSPLIT);
+                                mm(d + (C::NSPLIT + sp) * NTOK, a_gate + 2 * k, b + 2 * k, k >= C::NSPLIT);
                             }
                         } else {
                             const uint64_t a0 = make_smem_desc(st);
@@ -403,13 +415,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                             // tile t, operand half o (hi, lo): partial accumulator o when NSPLIT == 2, else both into one
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {
-                                umma_f8(d, a0 + 2 * k, bh + 2 * k, idesc, k > 0);
-                                umma_f8(d + C::NSPLIT * NTOK, a1 + 2 * k, bh + 2 * k, idesc, k > 0);
+                                mm(d, a0 + 2 * k, bh + 2 * k, k > 0);
+                                mm(d + C::NSPLIT * NTOK, a1 + 2 * k, bh + 2 * k, k > 0);
                             }
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {
-                                umma_f8(d + (C::NSPLIT - 1) * NTOK, a0 + 2 * k, bl + 2 * k, idesc, C::NSPLIT == 1 || k > 0);
-                                umma_f8(d + (2 * C::NSPLIT - 1) * NTOK, a1 + 2 * k, bl + 2 * k, idesc, C::NSPLIT == 1 || k > 0);
+                                mm(d + (C::NSPLIT - 1) * NTOK, a0 + 2 * k, bl + 2 * k, C::NSPLIT == 1 || k > 0);
+                                mm(d + (2 * C::NSPLIT - 1) * NTOK, a1 + 2 * k, bl + 2 * k, C::NSPLIT == 1 || k > 0);
                             }
                         }
                         umma_commit(bar_empty + 8 * stage);
@@ -440,7 +452,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         const uint32_t my_red = bar_red + 8 * grp_id;
         int stage = 0; uint32_t phase = 0;
         int ab = 0; uint32_t aphase = 0;
-        uint32_t rphase = 0;
+        uint32_t rphase = 0, allphase = 0;
         bool ok = true, seen = false;
         int ng = 0;
         float acc[C::NACCUM][C::NC];
@@ -451,6 +463,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             if (lane == 0) mbar_arrive(my_red);
             const bool r = mbar_wait(my_red, rphase, p.status, ERR_WAIT_GROUP);
             rphase ^= 1;
+            return r;
+        };
+
+        // all promotion warps meet (bounded); false = gave up
+        auto all_sync = [&]() -> bool {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_all);
+            const bool r = mbar_wait(bar_all, allphase, p.status, ERR_WAIT_GROUP);
+            allphase ^= 1;
             return r;
         };
 
@@ -528,6 +549,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 constexpr int NCH = C::NC / C::CH;
                 constexpr int NK = C::KPB * NCH * C::NACCUM * C::NSPLIT;
                 float part[2][C::CH];
+                float stok = 0.f;                 // tokens-on-M: this thread's token scale for the K block
                 if (!(kAblate & 2)) tmem_ld_chunk<C::CH>(tbuf, part[0]);
 #pragma unroll
                 for (int k = 0; k < NK; ++k) {
@@ -563,17 +585,30 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                                 // token scales of this K block arrived with the stage's transaction barrier
                                 const uint32_t ph = (st0 + j >= C::STAGES) ? (phase ^ 1) : phase;
                                 if (!mbar_wait(bar_full + 8 * sj, ph, p.status, ERR_WAIT_SMEM_FULL)) ok = false;
+                                if (C::TOK_ON_M) stok = reinterpret_cast<const float*>(smem + sj * C::STAGE_BYTES + C::SC_OFF)[m];
                             }
-                            const float* scp = reinterpret_cast<const float*>(smem + sj * C::STAGE_BYTES + C::SC_OFF) + c0 + ch * C::CH;
+                            if (C::TOK_ON_M) {
+                                // this thread's row is one token: one scalar scale per K block and weight tile
+                                const float sx = stok * swa;
+                                const float2 s2 = make_float2(sx, sx);
 #pragma unroll
-                            for (int i = 0; i < C::CH; i += 4) {
-                                const float4 s4 = *reinterpret_cast<const float4*>(scp + i);
-                                const float2 m0 = __fmul2_rn(make_float2(s4.x, s4.y), make_float2(swa, swa));
-                                const float2 m1 = __fmul2_rn(make_float2(s4.z, s4.w), make_float2(swa, swa));
-                                float* ac = &acc[a][ch * C::CH + i];
-                                const float2 r0 = __ffma2_rn(make_float2(part[k & 1][i], part[k & 1][i + 1]), m0, make_float2(ac[0], ac[1]));
-                                const float2 r1 = __ffma2_rn(make_float2(part[k & 1][i + 2], part[k & 1][i + 3]), m1, make_float2(ac[2], ac[3]));
-                                ac[0] = r0.x; ac[1] = r0.y; ac[2] = r1.x; ac[3] = r1.y;
+                                for (int i = 0; i < C::CH; i += 2) {
+                                    float* ac = &acc[a][ch * C::CH + i];
+                                    const float2 r0 = __ffma2_rn(make_float2(part[k & 1][i], part[k & 1][i + 1]), s2, make_float2(ac[0], ac[1]));
+                                    ac[0] = r0.x; ac[1] = r0.y;
+                                }
+                            } else {
+                                const float* scp = reinterpret_cast<const float*>(smem + sj * C::STAGE_BYTES + C::SC_OFF) + c0 + ch * C::CH;
+#pragma unroll
+                                for (int i = 0; i < C::CH; i += 4) {
+                                    const float4 s4 = *reinterpret_cast<const float4*>(scp + i);
+                                    const float2 m0 = __fmul2_rn(make_float2(s4.x, s4.y), make_float2(swa, swa));
+                                    const float2 m1 = __fmul2_rn(make_float2(s4.z, s4.w), make_float2(swa, swa));
+                                    float* ac = &acc[a][ch * C::CH + i];
+                                    const float2 r0 = __ffma2_rn(make_float2(part[k & 1][i], part[k & 1][i + 1]), m0, make_float2(ac[0], ac[1]));
+                                    const float2 r1 = __ffma2_rn(make_float2(part[k & 1][i + 2], part[k & 1][i + 3]), m1, make_float2(ac[2], ac[3]));
+                                    ac[0] = r0.x; ac[1] = r0.y; ac[2] = r1.x; ac[3] = r1.y;
+                                }
                             }
                         }
                     }
@@ -659,7 +694,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             }
 
             if (ptid == 0) stamp(TR_REDUCED);
-            if (G1) {
+            if (C::TOK_ON_M && G1) {
+                // this thread: token row m, NC consecutive columns j of the 128-wide block -> SwiGLU, amax over
+                // the block (own columns, then the other column groups' threads of the same row), two e4m3
+                // terms, 16-byte stores
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < C::NC; ++i) {
+                    const float v = silu_f(acc[1][i]) * acc[0][i];
+                    acc[0][i] = v;
+                    amax = fmaxf(amax, fabsf(v));
+                }
+                float* redf = reinterpret_cast<float*>(s_red);            // [NGRP][128]
+                redf[grp_id * 128 + m] = amax;
+                if (!all_sync()) { ok = false; break; }
+#pragma unroll
+                for (int g2 = 0; g2 < C::NGRP; ++g2) amax = fmaxf(amax, redf[g2 * 128 + m]);
+                if (!all_sync()) { ok = false; break; }                   // redf is reused by the next unit
+                const float scale = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
+                const float inv = amax > 0.f ? 448.0f / amax : 0.f;
+                if (m < un.nvalid) {
+                    const size_t row = (size_t)(un.row0 + m);
+                    uint4* dhi = reinterpret_cast<uint4*>(p.act_hi + row * p.I + (size_t)un.mt * 128 + c0);
+                    uint4* dlo = reinterpret_cast<uint4*>(p.act_lo + row * p.I + (size_t)un.mt * 128 + c0);
+#pragma unroll
+                    for (int v4 = 0; v4 < C::NC / 16; ++v4) {
+                        uint32_t wh[4], wl[4];
+#pragma unroll
+                        for (int w4 = 0; w4 < 4; ++w4) {
+                            const int i = v4 * 16 + w4 * 4;
+                            const float q0 = acc[0][i] * inv, q1 = acc[0][i + 1] * inv;
+                            const float q2 = acc[0][i + 2] * inv, q3 = acc[0][i + 3] * inv;
+                            const uint16_t h01 = f32x2_to_e4m3x2(q0, q1), h23 = f32x2_to_e4m3x2(q2, q3);
+                            const float2 f01 = e4m3x2_to_f32x2(h01), f23 = e4m3x2_to_f32x2(h23);
+                            const uint16_t l01 = f32x2_to_e4m3x2(q0 - f01.x, q1 - f01.y);
+                            const uint16_t l23 = f32x2_to_e4m3x2(q2 - f23.x, q3 - f23.y);
+                            wh[w4] = (uint32_t)h01 | ((uint32_t)h23 << 16);
+                            wl[w4] = (uint32_t)l01 | ((uint32_t)l23 << 16);
+                        }
+                        dhi[v4] = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+                        dlo[v4] = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+                    }
+                    if (grp_id == 0) p.act_scale[(size_t)un.mt * p.rows_cap + row] = scale;
+                }
+            } else if (C::TOK_ON_M) {
+                if (m < un.nvalid) {
+                    const size_t row = (size_t)(un.row0 + m);
+                    const float w = __ldg(p.row_w + row);
+#pragma unroll
+                    for (int a = 0; a < C::NACCUM; ++a) {
+                        const int col0 = un.mt * p.unit_rows + a * p.gate_offset + c0;
+                        if (col0 < p.valid_rows) {
+                            float4* dst = reinterpret_cast<float4*>(p.y + row * p.H + col0);
+#pragma unroll
+                            for (int i = 0; i < C::NC; i += 4)
+                                dst[i >> 2] = make_float4(acc[a][i] * w, acc[a][i + 1] * w, acc[a][i + 2] * w, acc[a][i + 3] * w);
+                        }
+                    }
+                }
+            } else if (G1) {
                 // SwiGLU, then amax over the 128 rows of the tile for every token column
                 uint32_t* red = s_red + pw * C::NC;
 #pragma unroll
