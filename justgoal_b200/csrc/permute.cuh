@@ -121,9 +121,21 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const PlanPara
     const int ge = e + p.local_offset;
     const int chunk = (p.T + blockDim.x - 1) / blockDim.x;
     const int t0 = min(tid * chunk, p.T), t1 = min(t0 + chunk, p.T);
+    // the thread's chunk is one contiguous run of ints; read it in 16-byte pieces when it can be
+    // (independent loads in flight instead of one dependent scalar load per entry)
+    const int i0 = t0 * p.top_k, i1 = t1 * p.top_k;
+    const bool vec = (p.top_k & 3) == 0;
     int mine = 0;
-    for (int t = t0; t < t1; ++t)
-        for (int k = 0; k < p.top_k; ++k) mine += (p.topk_idx[(size_t)t * p.top_k + k] == ge);
+    if (vec) {
+        const int4* v = reinterpret_cast<const int4*>(p.topk_idx + i0);
+#pragma unroll 4
+        for (int q = 0; q < (i1 - i0) >> 2; ++q) {
+            const int4 x = __ldg(v + q);
+            mine += (x.x == ge) + (x.y == ge) + (x.z == ge) + (x.w == ge);
+        }
+    } else {
+        for (int i = i0; i < i1; ++i) mine += (p.topk_idx[i] == ge);
+    }
     s_scan[tid] = mine;
     __syncthreads();
     // inclusive Hillis-Steele scan over the per-thread counters
@@ -134,16 +146,15 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const PlanPara
         __syncthreads();
     }
     int r = row0 + s_scan[tid] - mine;
-    for (int t = t0; t < t1; ++t)
-        for (int k = 0; k < p.top_k; ++k) {
-            const size_t i = (size_t)t * p.top_k + k;
-            if (p.topk_idx[i] == ge) {
-                p.pair_row[i] = r;
-                p.row_token[r] = t;
-                p.row_w[r] = p.topk_w[i];
-                ++r;
-            }
+    if (mine == 0) return;
+    for (int i = i0; i < i1; ++i) {
+        if (__ldg(p.topk_idx + i) == ge) {
+            p.pair_row[i] = r;
+            p.row_token[r] = i / p.top_k;
+            p.row_w[r] = p.topk_w[i];
+            ++r;
         }
+    }
 }
 
 // Expert-sorted copy of the fp8 activations and of their scales: a_perm[row] = hidden[token],
