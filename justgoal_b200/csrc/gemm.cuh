@@ -72,7 +72,11 @@ struct GemmCfg {
     static constexpr int B_BYTES = NTOK * 128;
     static constexpr int SC_OFF = NA * A_BYTES + NB * B_BYTES;
     static constexpr int STAGE_BYTES = SC_OFF + 1024;
-    static constexpr int TX_BYTES = NA * A_BYTES + NB * B_BYTES + NTOK * 4;
+    // tokens-on-M tiles read their (per-thread scalar) token scale straight from global memory, one K
+    // block ahead; the others get the tile's NTOK scales copied into the stage
+    static constexpr bool SCALES_IN_STAGE = NTOK != 128;
+    static constexpr int TX_BYTES = NA * A_BYTES + NB * B_BYTES + (SCALES_IN_STAGE ? NTOK * 4 : 0);
+    static constexpr int EMPTY_COUNT = 1 + (SCALES_IN_STAGE ? (NTOK >= 64 ? 8 : 4) : 0);   // MMA commit (+ promotion warps)
     static constexpr int STAGES_RAW = (208 * 1024) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int NACCUM = 2;                      // one accumulator per weight tile
@@ -96,6 +100,7 @@ struct GemmCfg {
     static constexpr int NPW = NTOK >= 64 ? 8 : 4;
     static constexpr int NGRP = NPW / 4;                   // column groups (a group = 4 warps = all 128 lanes)
     static constexpr int NPT = 32 * NPW;                   // promotion threads
+    static_assert(EMPTY_COUNT == 1 + (SCALES_IN_STAGE ? NPW : 0), "stage release count");
     static constexpr int NC = NTOK / (NPW / 4);            // token columns per promotion thread
     static constexpr int CH = (NACCUM * NC > 64) ? 16 : (NC < 32 ? NC : 32);   // columns per tcgen05.ld
     static constexpr int NTHREADS = 128 + NPT;
@@ -263,7 +268,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     static_assert(8 * (2 * C::STAGES + 2 * C::NACC + 5) <= 240, "barrier area");
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, 1 + C::NPW); }
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, C::EMPTY_COUNT); }
         for (int b = 0; b < C::NACC; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, C::NPW); }
         for (int g = 0; g < 4; ++g) mbar_init(bar_red + 8 * g, 4);
         mbar_init(bar_all, C::NPW);
@@ -346,7 +351,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     if (!(kAblate & 4)) {
                         tma_load_2d(st + C::NA * C::A_BYTES, &tm_b0, kb * 128, un.row0, full);
                         if (!G1) tma_load_2d(st + C::NA * C::A_BYTES + C::B_BYTES, &tm_b1, kb * 128, un.row0, full);
-                        bulk_load(st + C::SC_OFF, p.b_scale + (size_t)kb * p.rows_cap + un.row0, NTOK * 4, full);
+                        if (C::SCALES_IN_STAGE)
+                            bulk_load(st + C::SC_OFF, p.b_scale + (size_t)kb * p.rows_cap + un.row0, NTOK * 4, full);
                     }
                     if (!issued) { stamp(TR_TMA_FIRST); issued = true; }
                     klog_put(0, nk++);
@@ -376,7 +382,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     const int kb_end = min(p.KB, ge * C::KPB);
                     for (int kb = gb * C::KPB; kb < kb_end && ok; ++kb) {
                         if (!mbar_wait(bar_full + 8 * stage, phase, p.status, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
-                        for (int i = 0; i < 1 + C::NPW; ++i) mbar_arrive(bar_empty + 8 * stage);
+                        for (int i = 0; i < C::EMPTY_COUNT; ++i) mbar_arrive(bar_empty + 8 * stage);
                         if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                     }
                     continue;
@@ -501,6 +507,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 swn[j][0] = __ldg(ws0 + kb);
                 swn[j][1] = __ldg(ws1 + kb);
             }
+            // tokens-on-M: this thread's token scale, also one K block ahead (KPB == 1 there)
+            const float* tsp = p.b_scale + (size_t)un.row0 + m;
+            float stokn = C::TOK_ON_M ? __ldcg(tsp + (size_t)min(gb * C::KPB, p.KB - 1) * p.rows_cap) : 0.f;
             for (int grp = gb; grp < ge; ++grp) {
                 const int kb0 = grp * C::KPB;
                 const int nj = min(C::KPB, p.KB - kb0);
@@ -512,6 +521,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     swn[j][0] = __ldg(ws0 + kb);
                     swn[j][1] = __ldg(ws1 + kb);
                 }
+                const float stok_cur = stokn;
+                if (C::TOK_ON_M) stokn = __ldcg(tsp + (size_t)min(kb0 + 1, p.KB - 1) * p.rows_cap);
                 const int st0 = stage;
                 float scr[C::EARLY_SCALES ? C::KPB : 1][C::EARLY_SCALES ? C::NC : 1];
                 if (C::EARLY_SCALES && !(kAblate & 2)) {
@@ -549,7 +560,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 constexpr int NCH = C::NC / C::CH;
                 constexpr int NK = C::KPB * NCH * C::NACCUM * C::NSPLIT;
                 float part[2][C::CH];
-                float stok = 0.f;                 // tokens-on-M: this thread's token scale for the K block
                 if (!(kAblate & 2)) tmem_ld_chunk<C::CH>(tbuf, part[0]);
 #pragma unroll
                 for (int k = 0; k < NK; ++k) {
@@ -581,15 +591,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                             }
                         } else {
                             int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
-                            if (ch == 0 && a == 0 && sp == 0) {
+                            if (C::SCALES_IN_STAGE && ch == 0 && a == 0 && sp == 0) {
                                 // token scales of this K block arrived with the stage's transaction barrier
                                 const uint32_t ph = (st0 + j >= C::STAGES) ? (phase ^ 1) : phase;
                                 if (!mbar_wait(bar_full + 8 * sj, ph, p.status, ERR_WAIT_SMEM_FULL)) ok = false;
-                                if (C::TOK_ON_M) stok = reinterpret_cast<const float*>(smem + sj * C::STAGE_BYTES + C::SC_OFF)[m];
                             }
                             if (C::TOK_ON_M) {
                                 // this thread's row is one token: one scalar scale per K block and weight tile
-                                const float sx = stok * swa;
+                                const float sx = stok_cur * swa;
                                 const float2 s2 = make_float2(sx, sx);
 #pragma unroll
                                 for (int i = 0; i < C::CH; i += 2) {
@@ -619,7 +628,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(bar_tempty + 8 * ab);
-                    if (!C::EARLY_SCALES || (kAblate & 2)) {
+                    if (C::SCALES_IN_STAGE && (!C::EARLY_SCALES || (kAblate & 2))) {
                         for (int j = 0; j < nj; ++j) {
                             int sj = st0 + j; if (sj >= C::STAGES) sj -= C::STAGES;
                             mbar_arrive(bar_empty + 8 * sj);
