@@ -724,14 +724,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 const float inv = amax > 0.f ? 448.0f / amax : 0.f;
                 if (m < un.nvalid) {
                     const size_t row = (size_t)(un.row0 + m);
-                    uint4* dhi = reinterpret_cast<uint4*>(p.act_hi + row * p.I + (size_t)un.mt * 128 + c0);
-                    uint4* dlo = reinterpret_cast<uint4*>(p.act_lo + row * p.I + (size_t)un.mt * 128 + c0);
+                    uint8_t* dhi = p.act_hi + row * p.I + (size_t)un.mt * 128 + c0;
+                    uint8_t* dlo = p.act_lo + row * p.I + (size_t)un.mt * 128 + c0;
 #pragma unroll
-                    for (int v4 = 0; v4 < C::NC / 16; ++v4) {
-                        uint32_t wh[4], wl[4];
+                    for (int v8 = 0; v8 < C::NC / 32; ++v8) {
+                        uint32_t wh[8], wl[8];
 #pragma unroll
-                        for (int w4 = 0; w4 < 4; ++w4) {
-                            const int i = v4 * 16 + w4 * 4;
+                        for (int w4 = 0; w4 < 8; ++w4) {
+                            const int i = v8 * 32 + w4 * 4;
                             const float q0 = acc[0][i] * inv, q1 = acc[0][i + 1] * inv;
                             const float q2 = acc[0][i + 2] * inv, q3 = acc[0][i + 3] * inv;
                             const uint16_t h01 = f32x2_to_e4m3x2(q0, q1), h23 = f32x2_to_e4m3x2(q2, q3);
@@ -741,8 +741,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                             wh[w4] = (uint32_t)h01 | ((uint32_t)h23 << 16);
                             wl[w4] = (uint32_t)l01 | ((uint32_t)l23 << 16);
                         }
-                        dhi[v4] = make_uint4(wh[0], wh[1], wh[2], wh[3]);
-                        dlo[v4] = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+                        st_global_v8(dhi + v8 * 32, wh[0], wh[1], wh[2], wh[3], wh[4], wh[5], wh[6], wh[7]);
+                        st_global_v8(dlo + v8 * 32, wl[0], wl[1], wl[2], wl[3], wl[4], wl[5], wl[6], wl[7]);
                     }
                     if (grp_id == 0) p.act_scale[(size_t)un.mt * p.rows_cap + row] = scale;
                 }
@@ -754,10 +754,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     for (int a = 0; a < C::NACCUM; ++a) {
                         const int col0 = un.mt * p.unit_rows + a * p.gate_offset + c0;
                         if (col0 < p.valid_rows) {
-                            float4* dst = reinterpret_cast<float4*>(p.y + row * p.H + col0);
+                            float* dst = p.y + row * p.H + col0;
 #pragma unroll
-                            for (int i = 0; i < C::NC; i += 4)
-                                dst[i >> 2] = make_float4(acc[a][i] * w, acc[a][i + 1] * w, acc[a][i + 2] * w, acc[a][i + 3] * w);
+                            for (int i = 0; i < C::NC; i += 8)
+                                st_global_v8(dst + i, __float_as_uint(acc[a][i] * w), __float_as_uint(acc[a][i + 1] * w),
+                                             __float_as_uint(acc[a][i + 2] * w), __float_as_uint(acc[a][i + 3] * w),
+                                             __float_as_uint(acc[a][i + 4] * w), __float_as_uint(acc[a][i + 5] * w),
+                                             __float_as_uint(acc[a][i + 6] * w), __float_as_uint(acc[a][i + 7] * w));
                         }
                     }
                 }
