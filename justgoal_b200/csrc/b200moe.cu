@@ -146,7 +146,7 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     L->act_scale = take((size_t)(c.intermediate / 128) * rows * 4);
     L->y = take(rows * c.hidden * 4);
     L->sk_partial = take((size_t)2 * h->num_sms * SK_SLOT_FLOATS_MAX * 4);
-    L->trace = take((size_t)2 * h->num_sms * TRACE_SLOTS * 8 + 2 * 4 * KLOG_N * 8);   // [GEMM1 | GEMM2][CTA][slot], then K-block logs
+    L->trace = take((size_t)2 * h->num_sms * TRACE_SLOTS * 8 + 2 * 8 * KLOG_N * 8);   // [GEMM1 | GEMM2][CTA][slot], then K-block logs
     L->rows_cap = rows;
     L->token_tile = (size_t)pick_token_tile(c, T);
     L->total_bytes = off;
@@ -320,7 +320,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g2.sk_partial = g1.sk_partial;
     g2.ablate = (h->ablate >> 8) & 0xFF;
     g2.trace = g1.trace + (size_t)h->num_sms * TRACE_SLOTS;
-    g2.klog = g1.klog + 4 * KLOG_N;
+    g2.klog = g1.klog + 8 * KLOG_N;
     CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
     CU_TRY(prof_mark(h, 5, st));
 
@@ -381,8 +381,12 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     if (!h) return B200MOE_E_BADARG;
     h->cfg = *cfg; h->device = dev; h->num_sms = sms;
     h->prof_slots = 0; h->prof_calls = 0; h->prof_events = nullptr;
+#ifdef B200MOE_ENABLE_ABLATE
     const char* ab = getenv("B200MOE_ABLATE");
     h->ablate = ab ? atoi(ab) : 0;
+#else
+    h->ablate = 0;      // the timing switches exist only in builds made for timing experiments
+#endif
     *out = h;
     return 0;
 }

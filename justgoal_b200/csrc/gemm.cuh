@@ -94,6 +94,10 @@ struct GemmCfg {
     static constexpr int BUFCOLS = KPB * CPB;               // TMEM columns per hand-off buffer
     static constexpr int NACC = (512 / BUFCOLS) > 4 ? 4 : (512 / BUFCOLS);
     static constexpr int TMEM_COLS = NACC * BUFCOLS;
+    // Measured and dropped: handing a GEMM1 K block over as two 128-column halves (N = 128 MMAs, four
+    // half-buffers in flight) - the N = 128 MMAs compete with the TMA fills for shared-memory bandwidth
+    // and a K block took 750 ns instead of 570 ns.
+    static constexpr int NTB = NACC;                        // TMEM hand-off barriers per direction
     // promotion warps.  Measured: the fold of a 128 x 256 fp32 block takes ~1.1 us however the
     // tcgen05.ld are chunked, batched or spread over 8 or 16 warps - it is bound by the TMEM read
     // rate (~128 KB per K block), not by instruction issue or load latency.
@@ -110,8 +114,8 @@ struct GemmCfg {
     // register count ptxas actually chose, by the host before the first launch).
     static constexpr bool REALLOC_REGS = NPW >= 8;
     static constexpr int LAUNCH_REGS = (65536 / NTHREADS) / 8 * 8;          // what __launch_bounds__(NTHREADS, 1) yields
-    static constexpr int CTRL_REGS = NPW == 16 ? 32 : 40;
-    static constexpr int PROMO_REGS = NPW == 16 ? 112 : 232;
+    static constexpr int CTRL_REGS = 40;      // measured: 24/240, 40/232, 56/224 and 72/216 run within 1 % of each other
+    static constexpr int PROMO_REGS = 232;
     static_assert(!REALLOC_REGS || 128 * CTRL_REGS + NPT * PROMO_REGS <= NTHREADS * LAUNCH_REGS,
                   "setmaxnreg.inc would wait forever: the control warps do not release enough registers");
     static_assert(!REALLOC_REGS || (CTRL_REGS <= LAUNCH_REGS && PROMO_REGS >= LAUNCH_REGS), "setmaxnreg direction");
@@ -235,7 +239,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tail = smem + C::STAGES * C::STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tail);     // full[S], empty[S], tfull[NACC], tempty[NACC], red[2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail);     // full[S], empty[S], tfull[NTB], tempty[NTB], red[2]
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tail + 240);
     int* s_tiles = reinterpret_cast<int*>(tail + 256);
     int* s_row0 = s_tiles + (MAX_LOCAL + 1);
@@ -262,14 +266,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     const uint32_t bar_full = smem_u32(bars);
     const uint32_t bar_empty = bar_full + 8 * C::STAGES;
     const uint32_t bar_tfull = bar_empty + 8 * C::STAGES;
-    const uint32_t bar_tempty = bar_tfull + 8 * C::NACC;
-    const uint32_t bar_red = bar_tempty + 8 * C::NACC;    // one per column group: its 4 warps meet here (bounded)
+    const uint32_t bar_tempty = bar_tfull + 8 * C::NTB;
+    const uint32_t bar_red = bar_tempty + 8 * C::NTB;    // one per column group: its 4 warps meet here (bounded)
     const uint32_t bar_all = bar_red + 8 * 4;             // all promotion warps meet here (tokens-on-M epilogue)
-    static_assert(8 * (2 * C::STAGES + 2 * C::NACC + 5) <= 240, "barrier area");
+    static_assert(8 * (2 * C::STAGES + 2 * C::NTB + 5) <= 240, "barrier area");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, C::EMPTY_COUNT); }
-        for (int b = 0; b < C::NACC; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, C::NPW); }
+        for (int b = 0; b < C::NTB; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, C::NPW); }
         for (int g = 0; g < 4; ++g) mbar_init(bar_red + 8 * g, 4);
         mbar_init(bar_all, C::NPW);
         mbar_fence_init();
@@ -316,8 +320,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     if (warp < 4) {
     // ================================================================ control warpgroup
     if (C::REALLOC_REGS) {
-        if (C::CTRL_REGS == 32) asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
-        else asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::CTRL_REGS));
     }
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -391,6 +394,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     if (!mbar_wait(bar_tempty + 8 * ab, aphase ^ 1, p.status, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
                     const int nj = min(C::KPB, p.KB - grp * C::KPB);
                     for (int j = 0; j < nj; ++j) {
+                        klog_put(6, nk);
                         if (!mbar_wait(bar_full + 8 * stage, phase, p.status, ERR_WAIT_SMEM_FULL)) { ok = false; break; }
                         if (!seen) { stamp(TR_MMA_FIRST); seen = true; }
                         klog_put(1, nk++);
@@ -403,6 +407,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                             else umma_f8(dd, wdesc, tdesc, idesc, accum);
                         };
                         if (kAblate & 1) {
+                        } else if (C::TOK_ON_M) {
+                            // The two weight tiles of a stage are adjacent in shared memory (256 rows of 128 B)
+                            // and so are their accumulators in TMEM: ONE N = 256 MMA per 32-byte K step covers
+                            // both.  (An N = 128 MMA reads 8 KB of operands per 64 tensor-pipe cycles, all the
+                            // shared-memory bandwidth of the SM: measured 75 cycles alone, slower beside TMA fills.)
+                            constexpr uint32_t idesc2 = make_idesc_f8(128, 256);
+                            const uint64_t w = make_smem_desc(st);
+                            const uint64_t th = make_smem_desc(st + 2 * C::A_BYTES);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) umma_f8(d, th + 2 * k, w + 2 * k, idesc2, k > 0);
+                            if (!G1) {      // GEMM2: the low-order term of the activation accumulates on top
+                                const uint64_t tl = make_smem_desc(st + 2 * C::A_BYTES + C::B_BYTES);
+#pragma unroll
+                                for (int k = 0; k < 4; ++k) umma_f8(d, tl + 2 * k, w + 2 * k, idesc2, 1u);
+                            }
                         } else if (G1) {
                             const uint64_t a_up = make_smem_desc(st);
                             const uint64_t a_gate = make_smem_desc(st + C::A_BYTES);
@@ -445,8 +464,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     } else {
         // ------------------------------------------------------------ promotion + epilogue
         if (C::REALLOC_REGS) {
-            if (C::PROMO_REGS == 112) asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
-            else asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+            asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::PROMO_REGS));
         }
         const int pw = warp - 4;
         const int quarter = warp & 3;                  // TMEM lanes [32*quarter, +32)
@@ -460,7 +478,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         int ab = 0; uint32_t aphase = 0;
         uint32_t rphase = 0, allphase = 0;
         bool ok = true, seen = false;
-        int ng = 0;
+        int ng = 0, nu = 0;
         float acc[C::NACCUM][C::NC];
 
         // the 4 warps of one column group meet (bounded); false = gave up
@@ -558,9 +576,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 // flattened chunk list (K block, column chunk, accumulator, partial); the tcgen05.ld of
                 // chunk k+1 is in flight while chunk k is folded into the accumulators
                 constexpr int NCH = C::NC / C::CH;
-                constexpr int NK = C::KPB * NCH * C::NACCUM * C::NSPLIT;
+                constexpr int NK = C::TOK_ON_M ? 0 : C::KPB * NCH * C::NACCUM * C::NSPLIT;
+                if constexpr (C::TOK_ON_M) {
+                    // Tokens on M: this thread's row is one token, so a K block folds with ONE scalar per
+                    // weight tile.  The block is read as 32-column chunks, two tcgen05.ld in flight per
+                    // wait (a wait covers every outstanding load, so depth comes from issuing in pairs).
+                    constexpr int QC = 32, QPA = C::NC / QC, NQ = C::NACCUM * QPA;
+                    static_assert(C::NC % QC == 0 && NQ % 2 == 0, "tokens-on-M chunking");
+                    float stg[2][QC];
+                    auto qaddr = [&](int q) { return tbuf + (q / QPA) * NTOK + (q % QPA) * QC; };
+                    auto qfold = [&](int q, const float* v) {
+                        const int a = q / QPA;
+                        const float sx = stok_cur * sw[0][a];
+                        const float2 s2 = make_float2(sx, sx);
+                        float* ac = &acc[a][(q % QPA) * QC];
+#pragma unroll
+                        for (int i = 0; i < QC; i += 2) {
+                            const float2 r0 = __ffma2_rn(make_float2(v[i], v[i + 1]), s2, make_float2(ac[i], ac[i + 1]));
+                            ac[i] = r0.x; ac[i + 1] = r0.y;
+                        }
+                    };
+                    // the buffer goes back to the MMA warp as soon as its last tcgen05.ld has
+                    // completed; the FMAs of the last chunks run after the release
+                    auto release = [&]() {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_tempty + 8 * ab);
+                    };
+                    // This one switch stays a run-time test of p.ablate (always 0 outside timing experiments)
+                    // in every build: with the fold inside a real branch the compiler's schedule of this
+                    // kernel is measurably better (prefill layer 921 -> 897 us, same results bit for bit).
+                    if (p.ablate & 2) {
+                        release();
+                    } else {
+                        tmem_ld_chunk<QC>(qaddr(0), stg[0]);
+                        tmem_ld_chunk<QC>(qaddr(1), stg[1]);
+#pragma unroll
+                        for (int q = 0; q < NQ; q += 2) {
+                            tmem_wait_ld();
+                            if (q + 2 >= NQ) release();
+                            qfold(q, stg[0]);
+                            if (q + 2 < NQ) tmem_ld_chunk<QC>(qaddr(q + 2), stg[0]);
+                            qfold(q + 1, stg[1]);
+                            if (q + 3 < NQ) tmem_ld_chunk<QC>(qaddr(q + 3), stg[1]);
+                        }
+                    }
+                }
                 float part[2][C::CH];
-                if (!(kAblate & 2)) tmem_ld_chunk<C::CH>(tbuf, part[0]);
+                if (!C::TOK_ON_M && !(kAblate & 2)) tmem_ld_chunk<C::CH>(tbuf, part[0]);
 #pragma unroll
                 for (int k = 0; k < NK; ++k) {
                     const int sp = k % C::NSPLIT;
@@ -596,17 +659,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                                 const uint32_t ph = (st0 + j >= C::STAGES) ? (phase ^ 1) : phase;
                                 if (!mbar_wait(bar_full + 8 * sj, ph, p.status, ERR_WAIT_SMEM_FULL)) ok = false;
                             }
-                            if (C::TOK_ON_M) {
-                                // this thread's row is one token: one scalar scale per K block and weight tile
-                                const float sx = stok_cur * swa;
-                                const float2 s2 = make_float2(sx, sx);
-#pragma unroll
-                                for (int i = 0; i < C::CH; i += 2) {
-                                    float* ac = &acc[a][ch * C::CH + i];
-                                    const float2 r0 = __ffma2_rn(make_float2(part[k & 1][i], part[k & 1][i + 1]), s2, make_float2(ac[0], ac[1]));
-                                    ac[0] = r0.x; ac[1] = r0.y;
-                                }
-                            } else {
+                            {
                                 const float* scp = reinterpret_cast<const float*>(smem + sj * C::STAGE_BYTES + C::SC_OFF) + c0 + ch * C::CH;
 #pragma unroll
                                 for (int i = 0; i < C::CH; i += 4) {
@@ -624,9 +677,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 }
                 if (!ok) break;
                 // all tcgen05.ld of this buffer have completed (the last wait above) and all scale reads are done
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
+                if (!C::TOK_ON_M) {
+                    tc_fence_before();
+                    __syncwarp();
+                }
+                if (!C::TOK_ON_M && lane == 0) {
                     mbar_arrive(bar_tempty + 8 * ab);
                     if (C::SCALES_IN_STAGE && (!C::EARLY_SCALES || (kAblate & 2))) {
                         for (int j = 0; j < nj; ++j) {
@@ -702,7 +757,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 }
             }
 
-            if (ptid == 0) stamp(TR_REDUCED);
+            if (ptid == 0) { stamp(TR_REDUCED); klog_put(4, nu); }
             if (C::TOK_ON_M && G1) {
                 // this thread: token row m, NC consecutive columns j of the 128-wide block -> SwiGLU, amax over
                 // the block (own columns, then the other column groups' threads of the same row), two e4m3
@@ -818,6 +873,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     }
                 }
             }
+            if (ptid == 0) klog_put(5, nu++);
         }
     }
 
