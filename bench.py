@@ -178,12 +178,13 @@ def run_ours(args):
         out = layer.forward(*op)
     torch.cuda.synchronize()
     clocks = sampler.stop()
-    stage = {k: 0.0 for k in layer.STAGES}
-    for s in range(slots):
-        r = layer.profile_read(s)
-        for k in stage:
-            stage[k] += r[k] / slots
+    # median over the recorded steps: a stage's event pair also spans any host-side stall between
+    # its two records, and one such outlier must not move the roofline figure
+    per_slot = [layer.profile_read(s) for s in range(slots)]
+    stage = {k: sorted(r[k] for r in per_slot)[slots // 2] for k in layer.STAGES}
     layer.profile_enable(0)
+    if layer.status(T) != 0:
+        raise SystemExit(f"device error word {layer.status(T)} after the timed steps")
 
     # ---- end to end: host inputs -> device, forward, output -> host, every step
     host_in = [d[k].cpu().pin_memory() for k in ("routing_logits", "hidden_states", "hidden_states_scale")]

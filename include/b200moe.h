@@ -54,7 +54,7 @@ typedef struct b200moe_ctx* b200moe_handle;
 typedef struct b200moe_ws_layout {
     size_t status;        /* int32[8]: [0] device error word, [1] pairs P, [2] padded rows,
                              [3] token tiles, [4] active experts                           */
-    size_t counts;        /* int32[E_local] tokens per local expert                        */
+    size_t counts;        /* int32[E_local] tokens per local expert (sum of the slices)    */
     size_t expert_row0;   /* int32[E_local+1] first (padded) row of each expert            */
     size_t tile_prefix;   /* int32[E_local+1] exclusive prefix of token tiles              */
     size_t topk_idx;      /* int32[T, top_k] global expert ids                             */
@@ -69,6 +69,8 @@ typedef struct b200moe_ws_layout {
     size_t act_scale;     /* float[I/128, rows_cap]                                        */
     size_t y;             /* float[rows_cap, H] weighted expert outputs per row            */
     size_t sk_count;      /* int32[2][4*SMs] arrival counters of K-split units (GEMM1, GEMM2)*/
+    size_t slices;        /* int32[ceil(T*top_k/1024)][E_local] histogram of the local experts per
+                             slice of 1024 (token, expert) pairs, token-major                */
     size_t sk_partial;    /* float[2*SMs][32768] fp32 partial accumulators of K-split units */
     size_t trace;         /* int64[2][SMs][16] per-CTA time lines of GEMM1 and GEMM2: slot 0 =
                              %globaltimer at entry, slots 1..11 = SM clocks since entry at:

@@ -21,7 +21,7 @@ class Config(C.Structure):
 class WsLayout(C.Structure):
     _fields_ = [(n, C.c_size_t) for n in (
         "status", "counts", "expert_row0", "tile_prefix", "topk_idx", "topk_w", "pair_row", "row_token",
-        "row_w", "a_perm", "a_scale_perm", "act_hi", "act_lo", "act_scale", "y", "sk_count", "sk_partial", "trace",
+        "row_w", "a_perm", "a_scale_perm", "act_hi", "act_lo", "act_scale", "y", "sk_count", "slices", "sk_partial", "trace",
         "rows_cap", "token_tile",
         "total_bytes")]
 

@@ -107,6 +107,12 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Tokens per GEMM tile, from shapes only (never from data): the expected number of rows per
 // expert under uniform routing.
+// slices of SLICE_PAIRS (token, expert) pairs = CTAs of the permutation kernel (at least one)
+int num_slices(const b200moe_config& c, int T) {
+    const long long n = (long long)T * c.top_k;
+    return n <= 0 ? 1 : (int)((n + SLICE_PAIRS - 1) / SLICE_PAIRS);
+}
+
 int pick_token_tile(const b200moe_config& c, int T) {
     const double avg = (double)T * c.top_k / c.num_experts;
     if (avg <= 10.0) return 16;
@@ -132,6 +138,7 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     L->status = take(8 * 4);
     L->counts = take((size_t)El * 4);
     L->sk_count = take((size_t)2 * 4 * h->num_sms * 4);       // [GEMM1 | GEMM2][4 * grid]; zeroed with the head
+    L->slices = take((size_t)num_slices(c, T) * El * 4);      // zeroed with the head
     L->expert_row0 = take((size_t)(El + 1) * 4);
     L->tile_prefix = take((size_t)(El + 1) * 4);
     L->topk_idx = take((size_t)T * K * 4);
@@ -265,6 +272,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     PlanParams pp;
     pp.T = T; pp.top_k = c.top_k; pp.num_local = El; pp.local_offset = local_offset; pp.token_tile = ntok;
     pp.topk_idx = topk_idx; pp.topk_w = topk_w; pp.status = status; pp.counts = counts;
+    pp.slices = reinterpret_cast<const int*>(ws + L.slices);
     pp.expert_row0 = row0; pp.tile_prefix = tiles; pp.pair_row = pair_row; pp.row_token = row_token;
     pp.row_w = row_w; pp.rows_cap = rows_cap;
     if (fused_front) {
@@ -278,7 +286,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
         CU_TRY(prof_mark(h, 2, st));
         CU_TRY(prof_mark(h, 3, st));
     } else {
-        CU_TRY(launch_k(PDL_PERMUTE, permute_kernel, dim3(El), dim3(PERMUTE_THREADS), 0, st, pp));
+        CU_TRY(launch_k(PDL_PERMUTE, permute_kernel, dim3(num_slices(c, T)), dim3(PERMUTE_THREADS), 0, st, pp));
         CU_TRY(prof_mark(h, 2, st));
 
         const long long max_rows = (long long)T * (c.top_k < El ? c.top_k : El) + (long long)ROW_ALIGN * El;
@@ -337,10 +345,11 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
 }
 
 // ---- scratch of b200moe_permute_noalloc: lives in the library image of every device that
-// loads it.  Head: status int[8] at 0, counts int[256] at 256, tile_prefix int[257] at 1536;
-// then pair_row int[B200MOE_NOALLOC_MAX_TOKENS * 8] at 4096.
+// loads it.  Head: status int[8] at 0, counts int[256] at 256, tile_prefix int[257] at 1536; the
+// slice histograms int[64][256] at 4096; then pair_row int[B200MOE_NOALLOC_MAX_TOKENS * 8].
 constexpr size_t NOALLOC_HEAD_BYTES = 4096;
-constexpr size_t NOALLOC_SCRATCH_BYTES = NOALLOC_HEAD_BYTES + (size_t)B200MOE_NOALLOC_MAX_TOKENS * 8 * 4;
+constexpr size_t NOALLOC_SLICE_BYTES = (size_t)(B200MOE_NOALLOC_MAX_TOKENS * 8 / SLICE_PAIRS) * MAX_LOCAL * 4;
+constexpr size_t NOALLOC_SCRATCH_BYTES = NOALLOC_HEAD_BYTES + NOALLOC_SLICE_BYTES + (size_t)B200MOE_NOALLOC_MAX_TOKENS * 8 * 4;
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
 constexpr int NOALLOC_MAX_DEVICES = 64;
 unsigned char* g_noalloc_dev_ptr[NOALLOC_MAX_DEVICES];   // device address of the array, per device (host copy)
@@ -454,7 +463,7 @@ int b200moe_route(b200moe_handle h, const void* logits, const void* bias, int T,
     rp.logits = static_cast<const float*>(logits); rp.bias = static_cast<const __nv_bfloat16*>(bias);
     rp.T = T; rp.E = c.num_experts; rp.top_k = c.top_k; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
     rp.local_offset = 0; rp.num_local = 0; rp.scale = scale; rp.topk_idx = topk_idx; rp.topk_w = topk_w;
-    rp.counts = nullptr;
+    rp.slices = nullptr;
     CU_TRY(do_route(c, rp, static_cast<cudaStream_t>(stream)));
     return 0;
 }
@@ -473,7 +482,7 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     set_call_pdl(T);
-    // status + counts are contiguous at the head of the workspace: one memset clears both
+    // status, K-split counters and slice histograms are contiguous at the head of the workspace: one memset
     CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
     CU_TRY(prof_mark(h, 0, st));
     RouteParams rp;
@@ -481,9 +490,9 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     rp.T = T; rp.E = c.num_experts; rp.top_k = c.top_k; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
     rp.local_offset = local_offset; rp.num_local = c.num_local_experts; rp.scale = scale;
     rp.topk_idx = reinterpret_cast<int32_t*>(ws + L.topk_idx); rp.topk_w = reinterpret_cast<float*>(ws + L.topk_w);
-    rp.counts = reinterpret_cast<int*>(ws + L.counts);
+    rp.slices = reinterpret_cast<int*>(ws + L.slices);
     const bool fused = T <= FRONT_MAX_T;
-    if (fused) rp.counts = nullptr;       // the fused kernel builds the histogram itself
+    if (fused) rp.slices = nullptr;       // the fused kernel builds the histogram itself
     CU_TRY(do_route(c, rp, st));
     CU_TRY(prof_mark(h, 1, st));
     return run_experts(h, rp.topk_idx, rp.topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output,
@@ -511,7 +520,7 @@ int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const floa
     int grid = (n + 255) / 256;
     if (grid > h->num_sms * 4) grid = h->num_sms * 4;
     count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, local_offset, c.num_local_experts,
-                                       reinterpret_cast<int*>(ws + L.counts));
+                                       reinterpret_cast<int*>(ws + L.slices));
     CU_TRY(cudaGetLastError());
     CU_TRY(prof_mark(h, 1, st));
     return run_experts(h, topk_idx, topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output_f32,
@@ -544,12 +553,14 @@ int b200moe_permute_noalloc(b200moe_handle h, const int32_t* topk_idx, const flo
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int El = c.num_local_experts;
     // the histogram and the status words must start at zero; the array keeps the last call's contents
-    CU_TRY(cudaMemsetAsync(scratch, 0, NOALLOC_HEAD_BYTES, st));
+    const int ns = num_slices(c, T);
+    if (c.top_k > 8 || (size_t)ns * El * 4 > NOALLOC_SLICE_BYTES) return B200MOE_E_TOO_LARGE;
+    CU_TRY(cudaMemsetAsync(scratch, 0, NOALLOC_HEAD_BYTES + (size_t)ns * El * 4, st));
     if (T > 0) {
         const int n = T * c.top_k;
         int grid = (n + 255) / 256;
         if (grid > h->num_sms * 4) grid = h->num_sms * 4;
-        count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, local_offset, El, reinterpret_cast<int*>(scratch + 256));
+        count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, local_offset, El, reinterpret_cast<int*>(scratch + NOALLOC_HEAD_BYTES));
         CU_TRY(cudaGetLastError());
     }
     PlanParams pp;
@@ -559,9 +570,10 @@ int b200moe_permute_noalloc(b200moe_handle h, const int32_t* topk_idx, const flo
     pp.status = reinterpret_cast<int*>(scratch);
     pp.counts = reinterpret_cast<int*>(scratch + 256);
     pp.tile_prefix = reinterpret_cast<int*>(scratch + 1536);
-    pp.pair_row = reinterpret_cast<int32_t*>(scratch + NOALLOC_HEAD_BYTES);
+    pp.slices = reinterpret_cast<const int*>(scratch + NOALLOC_HEAD_BYTES);
+    pp.pair_row = reinterpret_cast<int32_t*>(scratch + NOALLOC_HEAD_BYTES + NOALLOC_SLICE_BYTES);
     pp.expert_row0 = expert_row0; pp.row_token = row_token; pp.row_w = row_w; pp.rows_cap = rows_capacity;
-    permute_kernel<<<El, PERMUTE_THREADS, 0, st>>>(pp);
+    permute_kernel<<<ns, PERMUTE_THREADS, 0, st>>>(pp);
     CU_TRY(cudaGetLastError());
     return 0;
 }

@@ -21,6 +21,10 @@ enum : int {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // every device-side wait gives up after 2 s
 
+// The (token, expert) pairs of a call, in token-major order, are cut into slices of SLICE_PAIRS pairs;
+// the routing kernel histograms every slice separately so that the permutation can run one CTA per slice.
+constexpr int SLICE_PAIRS = 1024;
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -528,6 +528,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             // tokens-on-M: this thread's token scale, also one K block ahead (KPB == 1 there)
             const float* tsp = p.b_scale + (size_t)un.row0 + m;
             float stokn = C::TOK_ON_M ? __ldcg(tsp + (size_t)min(gb * C::KPB, p.KB - 1) * p.rows_cap) : 0.f;
+            // GEMM2, tokens on M: the routing weight of this thread's row, fetched before the K loop
+            const float wrow = (C::TOK_ON_M && !G1 && m < un.nvalid) ? __ldg(p.row_w + un.row0 + m) : 0.f;
             for (int grp = gb; grp < ge; ++grp) {
                 const int kb0 = grp * C::KPB;
                 const int nj = min(C::KPB, p.KB - kb0);
@@ -802,9 +804,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     if (grp_id == 0) p.act_scale[(size_t)un.mt * p.rows_cap + row] = scale;
                 }
             } else if (C::TOK_ON_M) {
+                // 64 consecutive output columns of this thread's row per accumulator, as 256-bit stores.
+                // The 128 KB of a unit drain at ~32 B per cycle per SM (~2 us) whatever the pattern: a
+                // shuffle transpose that made every lane quad write 128 contiguous bytes was measured equal.
                 if (m < un.nvalid) {
                     const size_t row = (size_t)(un.row0 + m);
-                    const float w = __ldg(p.row_w + row);
 #pragma unroll
                     for (int a = 0; a < C::NACCUM; ++a) {
                         const int col0 = un.mt * p.unit_rows + a * p.gate_offset + c0;
@@ -812,10 +816,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                             float* dst = p.y + row * p.H + col0;
 #pragma unroll
                             for (int i = 0; i < C::NC; i += 8)
-                                st_global_v8(dst + i, __float_as_uint(acc[a][i] * w), __float_as_uint(acc[a][i + 1] * w),
-                                             __float_as_uint(acc[a][i + 2] * w), __float_as_uint(acc[a][i + 3] * w),
-                                             __float_as_uint(acc[a][i + 4] * w), __float_as_uint(acc[a][i + 5] * w),
-                                             __float_as_uint(acc[a][i + 6] * w), __float_as_uint(acc[a][i + 7] * w));
+                                st_global_v8(dst + i, __float_as_uint(acc[a][i] * wrow), __float_as_uint(acc[a][i + 1] * wrow),
+                                             __float_as_uint(acc[a][i + 2] * wrow), __float_as_uint(acc[a][i + 3] * wrow),
+                                             __float_as_uint(acc[a][i + 4] * wrow), __float_as_uint(acc[a][i + 5] * wrow),
+                                             __float_as_uint(acc[a][i + 6] * wrow), __float_as_uint(acc[a][i + 7] * wrow));
                         }
                     }
                 }

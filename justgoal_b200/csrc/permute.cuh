@@ -24,7 +24,8 @@ struct PlanParams {
     const int32_t* topk_idx;   // [T, top_k]
     const float* topk_w;       // [T, top_k]
     int* status;               // [8]
-    int* counts;               // [num_local]
+    const int* slices;         // [ceil(T*top_k / SLICE_PAIRS)][num_local] per-slice histogram (input)
+    int* counts;               // [num_local] (output: totals)
     int* expert_row0;          // [num_local + 1]
     int* tile_prefix;          // [num_local + 1]
     int32_t* pair_row;         // [T, top_k]
@@ -33,15 +34,15 @@ struct PlanParams {
     int rows_cap;
 };
 
-// Counts per local expert from an explicit topk_idx (the expert-parallel receive side, where
-// routing ran on another rank).
+// Per-slice histogram of the local experts from an explicit topk_idx (the expert-parallel receive
+// side, where routing ran on another rank); the routing kernel fills the same table itself.
 __global__ void count_kernel(const int32_t* __restrict__ topk_idx, int n, int local_offset, int num_local,
-                             int* __restrict__ counts) {
+                             int* __restrict__ slices) {
     pdl_wait();
     pdl_launch();
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const int le = topk_idx[i] - local_offset;
-        if (le >= 0 && le < num_local) atomicAdd(counts + le, 1);
+        if (le >= 0 && le < num_local) atomicAdd(slices + (size_t)(i / SLICE_PAIRS) * num_local + le, 1);
     }
 }
 
@@ -91,69 +92,77 @@ __device__ __forceinline__ void scan_counts(const int* counts, int num_local, in
     }
 }
 
-// One CTA per local expert.  Every CTA recomputes the (tiny) prefix over the counts, CTA 0
-// publishes it; then the CTA places its expert's pairs in token order.
-constexpr int PERMUTE_THREADS = 1024;
+// One CTA per slice of SLICE_PAIRS pairs, one thread per pair.  Every CTA sums the per-slice
+// histograms (totals -> the same scan in every CTA; slices before its own -> where its pairs start
+// inside each expert's segment), ranks its own pairs per expert in pair order (match + popcount inside
+// a warp, a prefix over the 32 warps) and places them.  No CTA waits for another; CTA 0 publishes the
+// tables and marks the padding rows.
+constexpr int PERMUTE_THREADS = SLICE_PAIRS;
 __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const PlanParams p) {
+    __shared__ int s_cnt[MAX_LOCAL];
+    __shared__ int s_before[MAX_LOCAL];
     __shared__ int s_row0[MAX_LOCAL + 1];
     __shared__ int s_tiles[MAX_LOCAL + 1];
-    __shared__ int s_scan[PERMUTE_THREADS];
-    const int e = blockIdx.x, tid = threadIdx.x;
+    __shared__ int s_wcnt[32][MAX_LOCAL + 1];      // [warp][expert]; odd stride: a column walk hits 32 banks
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int c = blockIdx.x, NS = gridDim.x, El = p.num_local;
+    const unsigned FULL = 0xFFFFFFFFu;
+    for (int i = tid; i < 32 * El; i += PERMUTE_THREADS) s_wcnt[i / El][i % El] = 0;
     pdl_wait();
     pdl_launch();
 
-    if (tid < 32) scan_counts(p.counts, p.num_local, p.token_tile, s_row0, s_tiles, e == 0 ? p.status : nullptr, tid);
-    __syncthreads();
-    if (e == 0) {
-        for (int i = tid; i <= p.num_local; i += blockDim.x) {
-            p.expert_row0[i] = s_row0[i];
-            p.tile_prefix[i] = s_tiles[i];
+    for (int e = warp; e < El; e += 32) {
+        int tot = 0, before = 0;
+        for (int s = lane; s < NS; s += 32) {
+            const int v = p.slices[(size_t)s * El + e];
+            tot += v;
+            if (s < c) before += v;
         }
+        for (int off = 16; off; off >>= 1) {
+            tot += __shfl_xor_sync(FULL, tot, off);
+            before += __shfl_xor_sync(FULL, before, off);
+        }
+        if (lane == 0) { s_cnt[e] = tot; s_before[e] = before; }
     }
-    const int cnt = p.counts[e];
-    const int row0 = s_row0[e];
-    const int row_end = s_row0[e + 1];
-    // padding rows of this segment carry token -1
-    for (int r = row0 + cnt + tid; r < row_end; r += blockDim.x) { p.row_token[r] = -1; p.row_w[r] = 0.f; }
-    if (cnt == 0) return;
+    __syncthreads();
+    if (warp == 0) scan_counts(s_cnt, El, p.token_tile, s_row0, s_tiles, c == 0 ? p.status : nullptr, lane);
 
-    // each thread owns a contiguous chunk of tokens -> order by token is preserved
-    const int ge = e + p.local_offset;
-    const int chunk = (p.T + blockDim.x - 1) / blockDim.x;
-    const int t0 = min(tid * chunk, p.T), t1 = min(t0 + chunk, p.T);
-    // the thread's chunk is one contiguous run of ints; read it in 16-byte pieces when it can be
-    // (independent loads in flight instead of one dependent scalar load per entry)
-    const int i0 = t0 * p.top_k, i1 = t1 * p.top_k;
-    const bool vec = (p.top_k & 3) == 0;
-    int mine = 0;
-    if (vec) {
-        const int4* v = reinterpret_cast<const int4*>(p.topk_idx + i0);
-#pragma unroll 4
-        for (int q = 0; q < (i1 - i0) >> 2; ++q) {
-            const int4 x = __ldg(v + q);
-            mine += (x.x == ge) + (x.y == ge) + (x.z == ge) + (x.w == ge);
-        }
-    } else {
-        for (int i = i0; i < i1; ++i) mine += (p.topk_idx[i] == ge);
-    }
-    s_scan[tid] = mine;
+    // this thread's pair: rank among the pairs of the same expert that precede it in the warp
+    const int n = p.T * p.top_k;
+    const int i = c * SLICE_PAIRS + tid;
+    const int le = i < n ? __ldg(p.topk_idx + i) - p.local_offset : -1;
+    const bool local = le >= 0 && le < El;
+    const unsigned same = __match_any_sync(FULL, local ? le : -1 - lane);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    if (local && rank == 0) s_wcnt[warp][le] = __popc(same);
     __syncthreads();
-    // inclusive Hillis-Steele scan over the per-thread counters
-    for (int off = 1; off < PERMUTE_THREADS; off <<= 1) {
-        const int add = tid >= off ? s_scan[tid - off] : 0;
-        __syncthreads();
-        s_scan[tid] += add;
-        __syncthreads();
-    }
-    int r = row0 + s_scan[tid] - mine;
-    if (mine == 0) return;
-    for (int i = i0; i < i1; ++i) {
-        if (__ldg(p.topk_idx + i) == ge) {
-            p.pair_row[i] = r;
-            p.row_token[r] = i / p.top_k;
-            p.row_w[r] = p.topk_w[i];
-            ++r;
+    // exclusive prefix over the warps, per expert: lane w of a warp holds warp w's count
+    for (int e = warp; e < El; e += 32) {
+        const int v = s_wcnt[lane][e];
+        int inc = v;
+        for (int off = 1; off < 32; off <<= 1) {
+            const int u = __shfl_up_sync(FULL, inc, off);
+            if (lane >= off) inc += u;
         }
+        s_wcnt[lane][e] = inc - v;
+    }
+    __syncthreads();
+
+    if (c == 0) {
+        for (int k = tid; k <= El; k += PERMUTE_THREADS) {
+            p.expert_row0[k] = s_row0[k];
+            p.tile_prefix[k] = s_tiles[k];
+            if (k < El) p.counts[k] = s_cnt[k];
+        }
+        // padding rows of every segment carry token -1
+        for (int e = warp; e < El; e += 32)
+            for (int r = s_row0[e] + s_cnt[e] + lane; r < s_row0[e + 1]; r += 32) { p.row_token[r] = -1; p.row_w[r] = 0.f; }
+    }
+    if (local) {
+        const int r = s_row0[le] + s_before[le] + s_wcnt[warp][le] + rank;
+        p.pair_row[i] = r;
+        p.row_token[r] = i / p.top_k;
+        p.row_w[r] = p.topk_w[i];
     }
 }
 

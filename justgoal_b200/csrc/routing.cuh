@@ -24,7 +24,7 @@ struct RouteParams {
     float scale;                  // routed scaling factor
     int32_t* topk_idx;            // [T, top_k]
     float* topk_w;                // [T, top_k]
-    int* counts;                  // [num_local] (+= 1 per local pair) or nullptr
+    int* slices;                  // [slices][num_local] histogram per slice of SLICE_PAIRS pairs (+= 1 per local pair) or nullptr
 };
 
 // Monotone map float -> uint32 (larger float <=> larger key); NaN ordering is unspecified.
@@ -136,7 +136,8 @@ __global__ void __launch_bounds__(256) route_kernel(const RouteParams p) {
         p.topk_idx[(size_t)t * p.top_k + lane] = sel_id;
         p.topk_w[(size_t)t * p.top_k + lane] = w;
         const int le = sel_id - p.local_offset;
-        if (p.counts && le >= 0 && le < p.num_local) atomicAdd(p.counts + le, 1);
+        if (p.slices && le >= 0 && le < p.num_local)
+            atomicAdd(p.slices + (size_t)((t * p.top_k + lane) / SLICE_PAIRS) * p.num_local + le, 1);
     }
 }
 
