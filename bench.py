@@ -256,7 +256,7 @@ def run_ours(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM1 launch, from the ncu capture
 # summarised under profiles/ (None until a capture of that workload exists)
-NCU_TRAFFIC = {"decode": 471.90e6 + 5.97e6, "prefill": 972.06e6 + 73.22e6}
+NCU_TRAFFIC = {"decode": 471.93e6 + 5.57e6, "prefill": 993.29e6 + 79.53e6}
 
 
 def _to_cpu(d):
