@@ -281,13 +281,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         if (!G1) tma_prefetch_desc(&tm_b1);
     }
     if (warp == 1) { tmem_alloc(smem_u32(s_tmem), C::TMEM_COLS); tmem_relinquish(); }
-    // Everything above touches only this CTA's shared memory and TMEM.  GEMM1 reads tables and rows that
-    // the kernel right before it wrote, so it waits here.  GEMM2 depends on GEMM1 only through the
-    // activation rows and their scales: the tables were complete before GEMM1 started (every kernel of
-    // the chain waits for its predecessor before it lets its successor launch), and the weights are
-    // inputs.  So GEMM2 reads the tables and starts streaming its first weight tiles while the last CTAs
-    // of GEMM1 are still running; only the token-side loads wait.
-    if (G1) pdl_wait();
+    // everything above touches only this CTA's shared memory and TMEM; the tables below are
+    // written by the kernels before this one
+    pdl_wait();
     pdl_launch();
     for (int i = threadIdx.x; i <= p.num_local; i += blockDim.x) {
         s_tiles[i] = p.tile_prefix[i];
@@ -333,33 +329,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             int stage = 0; uint32_t phase = 0;
             bool ok = true, issued = false;
             int nk = 0;
-            auto load_weights = [&](int sidx, int kb, int wrow) {
-                const uint32_t st = smem_base + sidx * C::STAGE_BYTES;
-                const uint32_t full = bar_full + 8 * sidx;
-                mbar_arrive_expect_tx(full, (kAblate & 4) ? C::NA * C::A_BYTES : C::TX_BYTES);
-                if (p.evict_first_weights) {
-                    tma_load_2d_hint(st, &tm_w, kb * 128, wrow, full, pol);
-                    tma_load_2d_hint(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full, pol);
-                } else {
-                    tma_load_2d(st, &tm_w, kb * 128, wrow, full);
-                    tma_load_2d(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full);
-                }
-            };
-            // GEMM2: the weight tiles of the first STAGES K blocks go out before the wait for GEMM1
-            int early = 0;
-            if (!G1) {
-                SkIter it0; it0.reset(sc);
-                SkSeg s0;
-                while (early < C::STAGES && it0.next(sc, s0)) {
-                    Unit un;
-                    if (!decode_unit(s0.u, p.n_mtiles, p.num_local, NTOK, s_tiles, s_row0, s_cnt, un)) break;
-                    const int wrow = un.e * p.rows_per_expert + un.mt * p.unit_rows;
-                    const int kb_end = min(p.KB, s0.ge * C::KPB);
-                    for (int kb = s0.gb * C::KPB; kb < kb_end && early < C::STAGES; ++kb, ++early) load_weights(early, kb, wrow);
-                }
-                pdl_wait();
-            }
-            int issued_kb = 0;
             SkIter it; it.reset(sc);
             SkSeg sg;
             while (ok && it.next(sc, sg)) {
@@ -371,13 +340,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 const int wrow = un.e * p.rows_per_expert + un.mt * p.unit_rows;
                 const int kb_end = min(p.KB, ge * C::KPB);
                 for (int kb = gb * C::KPB; kb < kb_end; ++kb) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, p.status, ERR_WAIT_SMEM_EMPTY)) { ok = false; break; }
                     const uint32_t st = smem_base + stage * C::STAGE_BYTES;
                     const uint32_t full = bar_full + 8 * stage;
-                    if (issued_kb >= early) {       // (the first `early` stages were empty and already have their weights)
-                        if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, p.status, ERR_WAIT_SMEM_EMPTY)) { ok = false; break; }
-                        load_weights(stage, kb, wrow);
+                    mbar_arrive_expect_tx(full, (kAblate & 4) ? C::NA * C::A_BYTES : C::TX_BYTES);
+                    if (p.evict_first_weights) {
+                        tma_load_2d_hint(st, &tm_w, kb * 128, wrow, full, pol);
+                        tma_load_2d_hint(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full, pol);
+                    } else {
+                        tma_load_2d(st, &tm_w, kb * 128, wrow, full);
+                        tma_load_2d(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full);
                     }
-                    ++issued_kb;
                     if (!(kAblate & 4)) {
                         tma_load_2d(st + C::NA * C::A_BYTES, &tm_b0, kb * 128, un.row0, full);
                         if (!G1) tma_load_2d(st + C::NA * C::A_BYTES + C::B_BYTES, &tm_b1, kb * 128, un.row0, full);
@@ -493,7 +466,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         if (C::REALLOC_REGS) {
             asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::PROMO_REGS));
         }
-        if (!G1) pdl_wait();      // GEMM2: the activation scales read below come from GEMM1
         const int pw = warp - 4;
         const int quarter = warp & 3;                  // TMEM lanes [32*quarter, +32)
         const int grp_id = pw >> 2;                    // column group (0 when NPW == 4)
