@@ -122,18 +122,27 @@ int b200moe_route(b200moe_handle h, const void* routing_logits, const void* rout
 
 /* The expert part alone, for tokens that were routed elsewhere (expert-parallel receive
  * side): like b200moe_forward but takes topk_idx/topk_w instead of logits, and writes the
- * fp32 sum over the LOCAL experts to output_f32 [T, H] (no bf16 rounding, so partial sums
- * of several ranks can be added before the single final rounding).  The reference has no
- * expert-parallel code; this corresponds to the launcher's stages after routing
- * (KF94/kernel.cu:5436-5586). */
+ * sum over the LOCAL experts to output [T, H]: fp32 when output_is_bf16 == 0 (no rounding,
+ * so partial sums of several ranks can be added before the single final rounding), bf16
+ * rows (one rounding of the local sum, the form that travels back over NVLink) otherwise.
+ * The reference has no expert-parallel code; this corresponds to the launcher's stages
+ * after routing (KF94/kernel.cu:5436-5586). */
 int b200moe_forward_routed(b200moe_handle h,
                            const int32_t* topk_idx, const float* topk_w,
                            const void* hidden_states, const void* hidden_states_scale,
                            const void* gemm1_weights, const void* gemm1_weights_scale,
                            const void* gemm2_weights, const void* gemm2_weights_scale,
                            int num_tokens, int local_expert_offset,
-                           float* output_f32, void* workspace, size_t workspace_bytes,
+                           void* output, int output_is_bf16, void* workspace, size_t workspace_bytes,
                            void* cuda_stream);
+
+/* Expert-parallel combine on the token's owner rank: out[t, :] = sum over the ranks r that
+ * computed a share of token t (row_of[r, t] >= 0) of partial_rows[row_of[r, t], :], added in
+ * fp32 in ascending rank order, rounded once to bf16.  partial_rows is the receive buffer
+ * of the combine all-to-all, bf16 [n_rows, H]; row_of is int32 [world, T].  Tokens without
+ * any share get zeros.  (No counterpart in the reference, which has no distributed code.) */
+int b200moe_ep_combine(b200moe_handle h, const void* partial_rows, const int32_t* row_of,
+                       int world, int num_tokens, void* output_bf16, void* cuda_stream);
 
 /* Expert-sorted row map without any workspace from the caller.  (No counterpart in the
  * reference: its launchers always receive caller-allocated workspaces.)

@@ -501,11 +501,11 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
 
 int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
                            const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2,
-                           int T, int local_offset, float* output_f32, void* workspace, size_t workspace_bytes,
-                           void* stream) {
+                           int T, int local_offset, void* output, int output_is_bf16, void* workspace,
+                           size_t workspace_bytes, void* stream) {
     if (!h || T < 0) return B200MOE_E_BADARG;
     if (T == 0) return 0;
-    if (!topk_idx || !topk_w || !hidden || !hidden_scale || !w13 || !s13 || !w2 || !s2 || !output_f32)
+    if (!topk_idx || !topk_w || !hidden || !hidden_scale || !w13 || !s13 || !w2 || !s2 || !output)
         return B200MOE_E_BADARG;
     b200moe_ws_layout L;
     int rc = check_ws(h, T, workspace, workspace_bytes, &L);
@@ -523,8 +523,22 @@ int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const floa
                                        reinterpret_cast<int*>(ws + L.slices));
     CU_TRY(cudaGetLastError());
     CU_TRY(prof_mark(h, 1, st));
-    return run_experts(h, topk_idx, topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output_f32,
-                       false, ws, L, st);
+    return run_experts(h, topk_idx, topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output,
+                       output_is_bf16 != 0, ws, L, st);
+}
+
+int b200moe_ep_combine(b200moe_handle h, const void* partial_rows, const int32_t* row_of, int world, int T,
+                       void* output_bf16, void* stream) {
+    if (!h || T < 0 || world < 1 || world > EP_MAX_WORLD) return B200MOE_E_BADARG;
+    if (T == 0) return 0;
+    if (!partial_rows || !row_of || !output_bf16) return B200MOE_E_BADARG;
+    const int H = h->cfg.hidden;
+    if (H % 8) return B200MOE_E_BADARG;
+    int grid = T < h->num_sms * 8 ? T : h->num_sms * 8;
+    ep_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(partial_rows), row_of, world, T, H, static_cast<__nv_bfloat16*>(output_bf16));
+    CU_TRY(cudaGetLastError());
+    return 0;
 }
 
 int b200moe_permute_noalloc(b200moe_handle h, const int32_t* topk_idx, const float* topk_w, int T, int local_offset,

@@ -246,4 +246,38 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
     }
 }
 
+// Expert-parallel combine on the owner rank: out[t] = sum over ranks r with row_of[r][t] >= 0 of
+// back[row_of[r][t]] (bf16 rows received from the ranks that own the token's experts), fp32, ascending
+// rank order, one rounding.  One CTA per token, 16 bytes per thread and step.
+constexpr int EP_MAX_WORLD = 64;
+__global__ void __launch_bounds__(256) ep_combine_kernel(const __nv_bfloat16* __restrict__ back,
+                                                         const int32_t* __restrict__ row_of, int world, int T, int H,
+                                                         __nv_bfloat16* __restrict__ out) {
+    __shared__ int s_row[EP_MAX_WORLD];
+    for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        __syncthreads();
+        if (threadIdx.x < world) s_row[threadIdx.x] = row_of[(size_t)threadIdx.x * T + t];
+        __syncthreads();
+        for (int h = threadIdx.x * 8; h < H; h += blockDim.x * 8) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < world; ++r) {
+                const int row = s_row[r];
+                if (row < 0) continue;
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(back + (size_t)row * H + h));
+                const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __bfloat1622float2(v2[q]);
+                    acc[2 * q] += f.x; acc[2 * q + 1] += f.y;
+                }
+            }
+            uint4 pk;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+            *reinterpret_cast<uint4*>(out + (size_t)t * H + h) = pk;
+        }
+    }
+}
+
 }  // namespace b200moe

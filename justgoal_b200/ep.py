@@ -27,25 +27,36 @@ from .inputs import MoEShape
 @dataclass
 class DispatchPlan:
     """Who gets which of my tokens.  `send_token[i]` is the local token of the i-th sent row; rows
-    are grouped by destination rank (ascending), tokens ascending inside a group."""
+    are grouped by destination rank (ascending), tokens ascending inside a group.  `row_of[r, t]`
+    is the sent row that carries token t to rank r (-1: rank r owns none of its experts) - the same
+    row index holds rank r's partial result in the buffer the combine all-to-all fills."""
     send_token: torch.Tensor        # int64 [n_send]
     send_counts: list               # rows per destination rank
     recv_counts: list               # rows per source rank
+    row_of: torch.Tensor            # int32 [world, T]
 
 
 def plan_dispatch(topk_idx: torch.Tensor, experts_per_rank: int, world: int, group=None) -> DispatchPlan:
     """De-duplicated per (token, destination rank): a token with several experts on one rank is
-    sent there once."""
-    dst = torch.div(topk_idx.long(), experts_per_rank, rounding_mode="floor")          # [T, K]
-    T = topk_idx.shape[0]
-    mask = torch.zeros(T, world, dtype=torch.bool, device=topk_idx.device)
-    mask.scatter_(1, dst.clamp_(0, world - 1), True)
-    pairs = torch.nonzero(mask.t(), as_tuple=False)                                     # (rank, token), sorted
-    send_counts = torch.bincount(pairs[:, 0], minlength=world)
+    sent there once.  One host synchronisation (the split sizes NCCL needs on the host)."""
+    T, dev = topk_idx.shape[0], topk_idx.device
+    dst = torch.div(topk_idx.long(), experts_per_rank, rounding_mode="floor").clamp_(0, world - 1)   # [T, K]
+    mask = torch.zeros(world, T, dtype=torch.int32, device=dev)
+    mask.scatter_(0, dst.t().contiguous(), 1)                     # mask[r, t] = 1 iff token t has an expert on rank r
+    within = torch.cumsum(mask, dim=1, dtype=torch.int32)         # inclusive rank of token t among rank r's rows
+    send_counts = within[:, -1].contiguous() if T else torch.zeros(world, dtype=torch.int32, device=dev)
     recv_counts = torch.empty_like(send_counts)
     dist.all_to_all_single(recv_counts, send_counts, group=group)
-    both = torch.stack([send_counts, recv_counts]).cpu()                                # the one host sync of a step
-    return DispatchPlan(pairs[:, 1].contiguous(), both[0].tolist(), both[1].tolist())
+    both = torch.stack([send_counts, recv_counts]).cpu()          # the one host sync of a step
+    send, recv = both[0].tolist(), both[1].tolist()
+    n_send = sum(send)
+    first = torch.cumsum(send_counts, 0, dtype=torch.int32) - send_counts          # first row of each destination
+    row_of = torch.where(mask.bool(), within - 1 + first[:, None], torch.full_like(within, -1))
+    # token of every sent row: scatter the token ids to their rows (non-pairs go to a spare slot)
+    slot = torch.where(row_of >= 0, row_of, torch.full_like(row_of, n_send)).long().reshape(-1)
+    tok_ids = torch.arange(T, device=dev, dtype=torch.int64).repeat(world)
+    send_token = torch.empty(n_send + 1, dtype=torch.int64, device=dev).scatter_(0, slot, tok_ids)[:n_send]
+    return DispatchPlan(send_token, send, recv, row_of)
 
 
 def _a2a(x: torch.Tensor, out_rows: int, in_splits, out_splits, group):
@@ -58,9 +69,11 @@ def _a2a(x: torch.Tensor, out_rows: int, in_splits, out_splits, group):
 
 
 class ExpertParallelMoE:
-    def __init__(self, shape: MoEShape, weights: dict, group=None, route_fn=None, experts_fn=None, device=None):
+    def __init__(self, shape: MoEShape, weights: dict, group=None, route_fn=None, experts_fn=None, combine_fn=None,
+                 device=None):
         """`shape.num_local_experts` experts per rank, rank r owning experts [r*E_local, (r+1)*E_local);
-        `weights` = this rank's gemm1/gemm2 weights and scales."""
+        `weights` = this rank's gemm1/gemm2 weights and scales.  `route_fn`, `experts_fn` and `combine_fn`
+        default to the CUDA library; the CPU tests of the exchange pass their own."""
         self.shape, self.group, self.w = shape, group, weights
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
@@ -68,11 +81,12 @@ class ExpertParallelMoE:
             raise ValueError("num_local_experts * world_size must equal num_experts")
         self.offset = self.rank * shape.num_local_experts
         self._layer = None
-        if route_fn is None or experts_fn is None:
+        if route_fn is None or experts_fn is None or combine_fn is None:
             from .main import MoELayer
             self._layer = MoELayer(shape, device)
         self.route_fn = route_fn or self._route_cuda
         self.experts_fn = experts_fn or self._experts_cuda
+        self.combine_fn = combine_fn or self._combine_cuda
         self.last_plan = None
 
     # ---- default local compute: the CUDA library
@@ -82,7 +96,10 @@ class ExpertParallelMoE:
     def _experts_cuda(self, idx, w, hidden, hscale):
         return self._layer.forward_routed(idx, w, hidden, hscale, self.w["gemm1_weights"],
                                           self.w["gemm1_weights_scale"], self.w["gemm2_weights"],
-                                          self.w["gemm2_weights_scale"], self.offset)
+                                          self.w["gemm2_weights_scale"], self.offset, out_dtype=torch.bfloat16)
+
+    def _combine_cuda(self, back, row_of, T):
+        return self._layer.ep_combine(back, row_of, T)
 
     # ---- one step
     @torch.no_grad()
@@ -91,11 +108,15 @@ class ExpertParallelMoE:
         [T_local, H], the full layer output for those tokens."""
         s, g = self.shape, self.group
         T, H = hidden_states.shape
+        mark = self._mark
+        mark("start")
         idx, w = self.route_fn(routing_logits, routing_bias, routed_scaling_factor)
+        mark("route")
         plan = plan_dispatch(idx, s.num_local_experts, self.world, g)
         self.last_plan = plan
         tok = plan.send_token
         n_recv = sum(plan.recv_counts)
+        mark("plan")
         # DISPATCH: rows, scales (token-major on the wire), ids and weights of every sent token
         x_send = hidden_states.view(torch.uint8).index_select(0, tok).view(torch.float8_e4m3fn)
         sc_send = hidden_states_scale.t().index_select(0, tok).contiguous()
@@ -105,16 +126,41 @@ class ExpertParallelMoE:
         sc_recv = _a2a(sc_send, n_recv, plan.send_counts, plan.recv_counts, g)
         idx_recv = _a2a(idx_send, n_recv, plan.send_counts, plan.recv_counts, g)
         w_recv = _a2a(w_send, n_recv, plan.send_counts, plan.recv_counts, g)
-        # LOCAL EXPERTS: fp32 sum over this rank's experts for every received token
+        mark("dispatch")
+        # LOCAL EXPERTS: sum over this rank's experts for every received token, as bf16 rows
         if n_recv:
             part = self.experts_fn(idx_recv, w_recv, x_recv, sc_recv.t().contiguous())
         else:
-            part = torch.zeros(0, H, dtype=torch.float32, device=hidden_states.device)
+            part = torch.zeros(0, H, dtype=torch.bfloat16, device=hidden_states.device)
+        if part.dtype != torch.bfloat16:
+            part = part.to(torch.bfloat16)
+        mark("experts")
         # COMBINE: bf16 partial rows back to the owners, fp32 sum over destination ranks, one rounding
-        back = _a2a(part.to(torch.bfloat16), tok.numel(), plan.recv_counts, plan.send_counts, g)
-        out = torch.zeros(T, H, dtype=torch.float32, device=hidden_states.device)
-        out.index_add_(0, tok, back.float())
-        return out.to(torch.bfloat16)
+        back = _a2a(part, tok.numel(), plan.recv_counts, plan.send_counts, g)
+        out = self.combine_fn(back, plan.row_of, T)
+        mark("combine")
+        return out
+
+    # ---- optional phase timing (CUDA events on the current stream; off unless `phase_events` is a list)
+    phase_events = None
+
+    def _mark(self, name):
+        if self.phase_events is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.phase_events.append((name, e))
+
+    def phase_ms(self):
+        """Durations between consecutive marks of the steps recorded since `phase_events = []`."""
+        torch.cuda.synchronize()
+        acc, n = {}, 0
+        ev = self.phase_events or []
+        for (n0, e0), (n1, e1) in zip(ev, ev[1:]):
+            if n1 == "start":
+                continue
+            acc[n1] = acc.get(n1, 0.0) + e0.elapsed_time(e1)
+            n += n1 == "combine"
+        return {k: v / max(n, 1) for k, v in acc.items()}
 
     def nvlink_bytes(self):
         """Bytes this rank sent to OTHER ranks in the last step (dispatch + combine partials received
@@ -173,8 +219,16 @@ def bench(args, spec, name, rank, world, local):
         nonlocal out
         out = ep.forward(logits, bias, hidden, hscale, spec["rsf"])
 
+    sync_time(step, 2)           # untimed: first use of the barrier / all-reduce / event path itself
     ms_step = sync_time(step, K)
     nv = ep.nvlink_bytes()
+    phases = None
+    if torch.cuda.is_available():
+        ep.phase_events = []
+        for _ in range(min(K, 10)):
+            step()
+        phases = ep.phase_ms()
+        ep.phase_events = None
 
     host_in = [t.cpu().pin_memory() for t in (logits, hidden, hscale)]
     dev_in = [torch.empty_like(t) for t in (logits, hidden, hscale)]
@@ -219,6 +273,7 @@ def bench(args, spec, name, rank, world, local):
                          "t_nvlink_ms": float(link) / 770e9 * 1e3},
             "layer": {"flops": flops, "tflops": flops / (ms_step * 1e-3) / 1e12, "pairs": float(pairs),
                       "rows_dispatched": float(n_recv), "max_link_bytes_per_rank": float(link)},
+            "phase_ms_rank0": phases,
         }
         print(json.dumps(line))
     dist.barrier()

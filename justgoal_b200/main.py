@@ -135,12 +135,15 @@ class MoELayer:
         return output
 
     def forward_routed(self, topk_idx, topk_w, hidden_states, hidden_states_scale, gemm1_weights,
-                       gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset, output=None):
-        """Expert part only, fp32 output (sum over the local experts, no bf16 rounding)."""
+                       gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset, output=None,
+                       out_dtype=torch.float32):
+        """Expert part only: the sum over the local experts, fp32 (no rounding) or bf16 rows."""
         s = self.shape
         T = int(hidden_states.shape[0])
         if output is None:
-            output = torch.empty(T, s.hidden, dtype=torch.float32, device=hidden_states.device)
+            output = torch.empty(T, s.hidden, dtype=out_dtype, device=hidden_states.device)
+        if output.dtype not in (torch.float32, torch.bfloat16) or not output.is_contiguous():
+            raise ValueError("output must be a contiguous fp32 or bf16 [T, hidden] tensor")
         if T == 0:
             return output
         if topk_idx.dtype != torch.int32 or topk_w.dtype != torch.float32:
@@ -150,10 +153,25 @@ class MoELayer:
                                         gemm1_weights_scale, gemm2_weights, gemm2_weights_scale)]
         stream = torch.cuda.current_stream(hidden_states.device).cuda_stream
         rc = _lib.lib.b200moe_forward_routed(self._h, *[_ptr(t) for t in tensors], T,
-                                             _scalar(local_expert_offset, int), _ptr(output), _ptr(ws),
+                                             _scalar(local_expert_offset, int), _ptr(output),
+                                             int(output.dtype == torch.bfloat16), _ptr(ws),
                                              ws.numel(), C.c_void_p(stream))
         _lib.check(rc, "b200moe_forward_routed")
         return output
+
+    def ep_combine(self, partial_rows, row_of, num_tokens):
+        """Owner-rank side of the expert-parallel combine: bf16 [T, hidden] = per token the fp32 sum, in
+        rank order, of the bf16 rows `partial_rows[row_of[r, t]]` (row_of int32 [world, T], -1 = none)."""
+        s = self.shape
+        world = int(row_of.shape[0])
+        if partial_rows.dtype != torch.bfloat16 or row_of.dtype != torch.int32 or row_of.shape[1] != num_tokens:
+            raise ValueError("partial_rows must be bf16 [n, hidden] and row_of int32 [world, T]")
+        out = torch.empty(num_tokens, s.hidden, dtype=torch.bfloat16, device=partial_rows.device)
+        stream = torch.cuda.current_stream(partial_rows.device).cuda_stream
+        rc = _lib.lib.b200moe_ep_combine(self._h, _ptr(_contig(partial_rows)), _ptr(_contig(row_of)), world,
+                                         int(num_tokens), _ptr(out), C.c_void_p(stream))
+        _lib.check(rc, "b200moe_ep_combine")
+        return out
 
     def route(self, routing_logits, routing_bias, routed_scaling_factor):
         s = self.shape

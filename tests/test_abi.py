@@ -19,7 +19,7 @@ def declared_functions():
 def test_header_declares_the_operator():
     names = declared_functions()
     for must in ("b200moe_create", "b200moe_destroy", "b200moe_workspace_bytes", "b200moe_forward",
-                 "b200moe_forward_routed", "b200moe_route", "b200moe_status"):
+                 "b200moe_forward_routed", "b200moe_ep_combine", "b200moe_route", "b200moe_status"):
         assert must in names
 
 

@@ -46,7 +46,15 @@ def _worker(rank, world, port, out_q):
                                       rank * shape.num_local_experts, shape.num_experts)
             return out
 
-        ep = ExpertParallelMoE(shape, weights, route_fn=route_fn, experts_fn=experts_fn)
+        def combine_fn(back, row_of, T):
+            # restatement of b200moe_ep_combine: fp32 sum in rank order, one rounding
+            acc = torch.zeros(T, back.shape[1], dtype=torch.float32)
+            for r in range(row_of.shape[0]):
+                has = row_of[r] >= 0
+                acc[has] += back[row_of[r][has].long()].float()
+            return acc.to(torch.bfloat16)
+
+        ep = ExpertParallelMoE(shape, weights, route_fn=route_fn, experts_fn=experts_fn, combine_fn=combine_fn)
         out = ep.forward(tokens["routing_logits"][sl], tokens["routing_bias"],
                          tokens["hidden_states"].view(torch.uint8)[sl].view(torch.float8_e4m3fn),
                          tokens["hidden_states_scale"][:, sl].contiguous(), RSF)

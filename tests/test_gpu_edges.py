@@ -1,0 +1,140 @@
+"""Ragged and boundary cases of the CUDA path against the oracle: one token, the first size past the
+fused small-T front end, several permutation slices, every token colliding on the same experts,
+ragged last tiles.  Output tolerance as stated for the operator; integer structures exact."""
+import pytest
+import torch
+
+import util
+from util import I, O
+
+pytestmark = pytest.mark.gpu
+
+
+def _forward(shape, d, layer=None):
+    from justgoal_b200 import MoELayer
+    layer = layer or MoELayer(shape)
+    out = layer.forward(*util.op_args(util.to_cuda(d)))
+    torch.cuda.synchronize()
+    T = int(d["hidden_states"].shape[0])
+    assert layer.status(T) == 0
+    return layer, out
+
+
+def _check_output(shape, d, out):
+    want = util.run_oracle(shape, d).output
+    rep = O.compare_output(out, want, util.ATOL, util.RTOL)
+    assert rep["fail_frac"] == 0.0, rep
+
+
+def _check_tables(shape, d, layer, T):
+    """counts, segment alignment, ascending tokens inside every expert segment, padding rows = -1,
+    pair_row pointing back at the pair's token."""
+    r = util.run_oracle(shape, d, keep_inter=True)
+    El, K = shape.num_local_experts, shape.top_k
+    rows_cap = int(layer.layout(T).rows_cap)
+    counts = layer.view(T, "counts", torch.int32, (El,)).cpu()
+    row0 = layer.view(T, "expert_row0", torch.int32, (El + 1,)).cpu()
+    row_token = layer.view(T, "row_token", torch.int32, (rows_cap,)).cpu()
+    pair_row = layer.view(T, "pair_row", torch.int32, (T, K)).cpu()
+    topk = layer.view(T, "topk_idx", torch.int32, (T, K)).cpu()
+    want = torch.tensor([len(r.expert_tokens.get(e, [])) for e in range(El)], dtype=torch.int32)
+    assert torch.equal(counts, want)
+    for e in range(El):
+        a, c = int(row0[e]), int(counts[e])
+        assert a % 16 == 0 and int(row0[e + 1]) - a == (c + 15) // 16 * 16
+        if c:
+            assert torch.equal(row_token[a:a + c].long(), r.expert_tokens[e])
+        assert bool((row_token[a + c:int(row0[e + 1])] == -1).all())
+    off = int(d["local_expert_offset"])
+    local = (topk >= off) & (topk < off + El)
+    t_of_pair = torch.arange(T).unsqueeze(1).expand(T, K)
+    assert torch.equal(row_token[pair_row[local].long()].long(), t_of_pair[local])
+
+
+def test_single_token():
+    shape = I.TINY_DS
+    d = I.make_inputs(shape, 1, seed=21)
+    layer, out = _forward(shape, d)
+    _check_output(shape, d, out)
+
+
+@pytest.mark.parametrize("T", [128, 129, 257])
+def test_around_the_fused_front_end_boundary(T):
+    """T = 128 is the last size of the fused permute + gather launch, 129 the first of the sliced
+    permutation (two slices of 1024 pairs), 257 crosses into a third slice."""
+    shape = I.TINY_DS
+    d = I.make_inputs(shape, T, seed=22 + T)
+    layer, out = _forward(shape, d)
+    _check_output(shape, d, out)
+    _check_tables(shape, d, layer, T)
+
+
+def test_many_slices_top4():
+    """top-4 shape, 700 tokens = 2800 pairs = 3 slices; a token's pairs straddle slice borders."""
+    shape = I.TINY_RENORM
+    d = I.make_inputs(shape, 700, seed=31)
+    layer, out = _forward(shape, d)
+    _check_output(shape, d, out)
+    _check_tables(shape, d, layer, 700)
+
+
+def test_all_tokens_collide_on_the_same_experts():
+    """Identical routing rows: every token picks the same top-k experts, so a few experts receive T
+    rows each (several token tiles with a ragged last one) and all others none."""
+    shape = I.TINY_DS
+    T = 300
+    d = I.make_inputs(shape, T, seed=41)
+    d["routing_logits"] = d["routing_logits"][:1].repeat(T, 1).contiguous()
+    layer, out = _forward(shape, d)
+    _check_output(shape, d, out)
+    _check_tables(shape, d, layer, T)
+    counts = layer.view(T, "counts", torch.int32, (shape.num_local_experts,)).cpu()
+    assert set(counts.tolist()) <= {0, T}
+
+
+def test_workspace_reuse_across_sizes():
+    """One layer object, shrinking and growing token counts back to back (workspace buckets, stale
+    tables from the larger call must not leak into the smaller one)."""
+    from justgoal_b200 import MoELayer
+    shape = I.TINY_DS
+    layer = MoELayer(shape)
+    for T, seed in ((513, 51), (5, 52), (130, 53), (64, 54)):
+        d = I.make_inputs(shape, T, seed=seed)
+        _, out = _forward(shape, d, layer)
+        _check_output(shape, d, out)
+
+
+def test_ep_combine_kernel_matches_restatement():
+    """b200moe_ep_combine: fp32 sum in rank order of the bf16 rows a token's ranks sent back."""
+    from justgoal_b200 import MoELayer
+    shape = I.TINY_DS
+    layer = MoELayer(shape)
+    T, world, H = 37, 4, shape.hidden
+    g = torch.Generator().manual_seed(61)
+    has = torch.rand(world, T, generator=g) < 0.6
+    has[:, 5] = False                                     # a token nobody computed: zeros
+    row_of = torch.full((world, T), -1, dtype=torch.int32)
+    row_of[has] = torch.arange(int(has.sum()), dtype=torch.int32)
+    back = torch.randn(int(has.sum()), H, generator=g).to(torch.bfloat16)
+    got = layer.ep_combine(back.cuda(), row_of.cuda(), T).cpu()
+    want = torch.zeros(T, H, dtype=torch.float32)
+    for r in range(world):
+        sel = row_of[r] >= 0
+        want[sel] += back[row_of[r][sel].long()].float()
+    assert torch.equal(got.view(torch.int16), want.to(torch.bfloat16).view(torch.int16))
+    assert bool((got[5].float() == 0).all())
+
+
+def test_forward_routed_bf16_is_the_rounded_fp32_result():
+    from justgoal_b200 import MoELayer
+    shape = I.TINY_DS
+    T = 45
+    d = util.to_cuda(I.make_inputs(shape, T, seed=62))
+    layer = MoELayer(shape)
+    idx, w = layer.route(d["routing_logits"], d["routing_bias"], d["routed_scaling_factor"])
+    args = (idx, w, d["hidden_states"], d["hidden_states_scale"], d["gemm1_weights"], d["gemm1_weights_scale"],
+            d["gemm2_weights"], d["gemm2_weights_scale"], d["local_expert_offset"])
+    f32 = layer.forward_routed(*args).clone()
+    b16 = layer.forward_routed(*args, out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    assert torch.equal(b16.view(torch.int16), f32.to(torch.bfloat16).view(torch.int16))
