@@ -136,6 +136,21 @@ int b200moe_forward_routed(b200moe_handle h,
                            void* output, int output_is_bf16, void* workspace, size_t workspace_bytes,
                            void* cuda_stream);
 
+/* Expert-parallel dispatch rows.  One row on the wire carries all a receiving rank needs for one
+ * token: [H fp8 bytes | H/128 fp32 scales | top_k int32 global expert ids | top_k fp32 weights],
+ * padded to a multiple of 16 bytes (b200moe_ep_row_bytes), so the dispatch is one all-to-all.
+ *   pack  : wire[i] = row of token send_token[i] (int64, 0 <= token < num_tokens), i < n_rows;
+ *           hidden_states fp8 [T, H], hidden_states_scale float [H/128, T], topk_* [T, top_k]
+ *   unpack: received wire rows -> hidden_states fp8 [n_rows, H], hidden_states_scale float
+ *           [H/128, n_rows], topk_idx / topk_w [n_rows, top_k] (inputs of b200moe_forward_routed)
+ * (No counterpart in the reference, which has no distributed code.) */
+int b200moe_ep_row_bytes(b200moe_handle h, int* bytes);
+int b200moe_ep_pack(b200moe_handle h, const void* hidden_states, const void* hidden_states_scale,
+                    const int32_t* topk_idx, const float* topk_w, const long long* send_token,
+                    int n_rows, int num_tokens, void* wire, void* cuda_stream);
+int b200moe_ep_unpack(b200moe_handle h, const void* wire, int n_rows, void* hidden_states,
+                      void* hidden_states_scale, int32_t* topk_idx, float* topk_w, void* cuda_stream);
+
 /* Expert-parallel combine on the token's owner rank: out[t, :] = sum over the ranks r that
  * computed a share of token t (row_of[r, t] >= 0) of partial_rows[row_of[r, t], :], added in
  * fp32 in ascending rank order, rounded once to bf16.  partial_rows is the receive buffer
@@ -153,7 +168,7 @@ int b200moe_ep_combine(b200moe_handle h, const void* partial_rows, const int32_t
  * sits between stream operations where a cudaMalloc would stall the device.  For them this
  * entry point does the histogram / scan / permute step (the same kernels b200moe_forward uses)
  * with its scratch -- histogram counters, tile prefix, status words and the token->row map --
- * in a fixed array inside the library image (about 260 KB per GPU that loads the library, held
+ * in a fixed array inside the library image (about 330 KB per GPU that loads the library, held
  * until the process exits).  It calls no cudaMalloc/cudaFree and no allocating routine.
  *
  *   in : topk_idx int32 [T, top_k], topk_w float [T, top_k], local_expert_offset

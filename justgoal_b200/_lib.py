@@ -40,6 +40,9 @@ def _load():
     lib.b200moe_route.argtypes = [vp, vp, vp, i, f, vp, vp, vp]
     lib.b200moe_forward_routed.argtypes = [vp, vp, vp] + [vp] * 6 + [i, i, vp, i, vp, sz, vp]
     lib.b200moe_ep_combine.argtypes = [vp, vp, vp, i, i, vp, vp]
+    lib.b200moe_ep_row_bytes.argtypes = [vp, C.POINTER(i)]
+    lib.b200moe_ep_pack.argtypes = [vp, vp, vp, vp, vp, vp, i, i, vp, vp]
+    lib.b200moe_ep_unpack.argtypes = [vp, vp, i, vp, vp, vp, vp, vp]
     lib.b200moe_status.argtypes = [vp, vp, vp, C.POINTER(i)]
     lib.b200moe_launches_per_forward.argtypes = [vp, i, C.POINTER(i)]
     lib.b200moe_permute_noalloc.argtypes = [vp, vp, vp, i, i, vp, vp, vp, i, vp]
@@ -50,7 +53,7 @@ def _load():
     lib.b200moe_num_sms.argtypes = []
     for name in ("create", "destroy", "workspace_bytes", "workspace_layout", "forward", "route",
                  "forward_routed", "status", "launches_per_forward", "num_sms", "profile_enable",
-                 "profile_read", "permute_noalloc", "ep_combine"):
+                 "profile_read", "permute_noalloc", "ep_combine", "ep_row_bytes", "ep_pack", "ep_unpack"):
         getattr(lib, "b200moe_" + name).restype = i
     return lib
 

@@ -527,6 +527,40 @@ int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const floa
                        output_is_bf16 != 0, ws, L, st);
 }
 
+int b200moe_ep_row_bytes(b200moe_handle h, int* bytes) {
+    if (!h || !bytes) return B200MOE_E_BADARG;
+    *bytes = ep_row_bytes(h->cfg.hidden, h->cfg.top_k);
+    return 0;
+}
+
+int b200moe_ep_pack(b200moe_handle h, const void* hidden, const void* hidden_scale, const int32_t* topk_idx,
+                    const float* topk_w, const long long* send_token, int n_rows, int T, void* wire, void* stream) {
+    if (!h || n_rows < 0 || T < 0 || h->cfg.top_k > 32) return B200MOE_E_BADARG;
+    if (n_rows == 0) return 0;
+    if (!hidden || !hidden_scale || !topk_idx || !topk_w || !send_token || !wire) return B200MOE_E_BADARG;
+    int grid = (n_rows + 7) / 8;
+    if (grid > h->num_sms * 8) grid = h->num_sms * 8;
+    ep_pack_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(hidden), static_cast<const float*>(hidden_scale), topk_idx, topk_w, send_token,
+        n_rows, T, h->cfg.hidden, h->cfg.top_k, static_cast<uint8_t*>(wire));
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
+int b200moe_ep_unpack(b200moe_handle h, const void* wire, int n_rows, void* hidden, void* hidden_scale,
+                      int32_t* topk_idx, float* topk_w, void* stream) {
+    if (!h || n_rows < 0 || h->cfg.top_k > 32) return B200MOE_E_BADARG;
+    if (n_rows == 0) return 0;
+    if (!wire || !hidden || !hidden_scale || !topk_idx || !topk_w) return B200MOE_E_BADARG;
+    int grid = (n_rows + 7) / 8;
+    if (grid > h->num_sms * 8) grid = h->num_sms * 8;
+    ep_unpack_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(wire), n_rows, h->cfg.hidden, h->cfg.top_k, static_cast<uint8_t*>(hidden),
+        static_cast<float*>(hidden_scale), topk_idx, topk_w);
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
 int b200moe_ep_combine(b200moe_handle h, const void* partial_rows, const int32_t* row_of, int world, int T,
                        void* output_bf16, void* stream) {
     if (!h || T < 0 || world < 1 || world > EP_MAX_WORLD) return B200MOE_E_BADARG;

@@ -710,13 +710,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                     for (int i = 0; i < C::NC; ++i) __stcg(slot + (size_t)(a * C::NC + i) * C::NPT + ptid, acc[a][i]);
                 __threadfence();
-                if (!group_sync()) { ok = false; break; }
-                if (quarter == 0 && lane == 0) {
-                    s_flag[grp_id] = atomicAdd(p.sk_count + c_first * 4 + grp_id, 1);
+                // Who is last is decided per column group where the epilogue works per group (weights on M),
+                // but ONCE PER CTA with tokens on M: that epilogue reduces across the column groups (all
+                // promotion warps meet), so all of them must agree on which CTA runs it.
+                auto meet = [&]() -> bool { return C::TOK_ON_M ? all_sync() : group_sync(); };
+                const int cnt_id = C::TOK_ON_M ? 0 : grp_id;
+                if (!meet()) { ok = false; break; }
+                if (quarter == 0 && lane == 0 && (!C::TOK_ON_M || grp_id == 0)) {
+                    s_flag[cnt_id] = atomicAdd(p.sk_count + c_first * 4 + cnt_id, 1);
                 }
-                if (!group_sync()) { ok = false; break; }
-                const bool last = s_flag[grp_id] == (c_last - c_first);
-                if (!group_sync()) { ok = false; break; }          // s_flag may be rewritten by the next split unit
+                if (!meet()) { ok = false; break; }
+                const bool last = s_flag[cnt_id] == (c_last - c_first);
+                if (!meet()) { ok = false; break; }                // s_flag may be rewritten by the next split unit
                 if (ptid == 0) stamp(TR_PARTIAL);
                 if (!last) continue;
                 __threadfence();

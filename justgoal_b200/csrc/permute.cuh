@@ -246,6 +246,53 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
     }
 }
 
+// Expert-parallel dispatch rows.  One row on the wire carries everything the receiving rank needs for
+// one token: [H fp8 bytes | H/128 fp32 scales | top_k int32 expert ids | top_k fp32 weights], padded to
+// 16 bytes - so the dispatch is ONE all-to-all instead of four.
+__host__ __device__ inline int ep_row_bytes(int H, int top_k) { return (H + 4 * (H >> 7) + 8 * top_k + 15) & ~15; }
+
+// pack: wire[i] = row of token send_token[i].  One warp per row.
+__global__ void __launch_bounds__(256) ep_pack_kernel(const uint8_t* __restrict__ hidden, const float* __restrict__ hscale,
+                                                      const int32_t* __restrict__ topk_idx, const float* __restrict__ topk_w,
+                                                      const long long* __restrict__ send_token, int n, int T, int H,
+                                                      int top_k, uint8_t* __restrict__ wire) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int KB = H >> 7, rb = ep_row_bytes(H, top_k);
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < n; i += warps) {
+        const int t = (int)send_token[i];
+        uint8_t* dst = wire + (size_t)i * rb;
+        const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * H);
+        for (int c = lane; c < H / 16; c += 32) reinterpret_cast<uint4*>(dst)[c] = __ldg(src + c);
+        float* ds = reinterpret_cast<float*>(dst + H);
+        for (int kb = lane; kb < KB; kb += 32) ds[kb] = __ldg(hscale + (size_t)kb * T + t);
+        if (lane < top_k) {
+            reinterpret_cast<int32_t*>(dst + H + 4 * KB)[lane] = topk_idx[(size_t)t * top_k + lane];
+            reinterpret_cast<float*>(dst + H + 4 * KB + 4 * top_k)[lane] = topk_w[(size_t)t * top_k + lane];
+        }
+    }
+}
+
+// unpack: the received rows back into the operator's layouts (scales K-block major).  One warp per row.
+__global__ void __launch_bounds__(256) ep_unpack_kernel(const uint8_t* __restrict__ wire, int n, int H, int top_k,
+                                                        uint8_t* __restrict__ hidden, float* __restrict__ hscale,
+                                                        int32_t* __restrict__ topk_idx, float* __restrict__ topk_w) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    const int KB = H >> 7, rb = ep_row_bytes(H, top_k);
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < n; i += warps) {
+        const uint8_t* src = wire + (size_t)i * rb;
+        uint4* dst = reinterpret_cast<uint4*>(hidden + (size_t)i * H);
+        for (int c = lane; c < H / 16; c += 32) dst[c] = __ldg(reinterpret_cast<const uint4*>(src) + c);
+        const float* ss = reinterpret_cast<const float*>(src + H);
+        for (int kb = lane; kb < KB; kb += 32) hscale[(size_t)kb * n + i] = ss[kb];
+        if (lane < top_k) {
+            topk_idx[(size_t)i * top_k + lane] = reinterpret_cast<const int32_t*>(src + H + 4 * KB)[lane];
+            topk_w[(size_t)i * top_k + lane] = reinterpret_cast<const float*>(src + H + 4 * KB + 4 * top_k)[lane];
+        }
+    }
+}
+
 // Expert-parallel combine on the owner rank: out[t] = sum over ranks r with row_of[r][t] >= 0 of
 // back[row_of[r][t]] (bf16 rows received from the ranks that own the token's experts), fp32, ascending
 // rank order, one rounding.  One CTA per token, 16 bytes per thread and step.

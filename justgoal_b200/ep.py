@@ -4,15 +4,15 @@ The reference corpus has no distributed code; its operator is ONE rank's share o
 (`local_expert_offset`, 32 local of 256 experts: goal_full_shape/fable-5.1/moe_fp8_fwd/<def>/
 moe_common.cuh:14-15).  This module supplies the two exchanges around that share:
 
-  route own tokens -> DISPATCH (all-to-all of fp8 rows + scales + the token's top-k ids/weights,
-  one copy per (token, destination rank)) -> local experts (b200moe_forward_routed: fp32 sum over
-  the local experts of a received token) -> COMBINE (all-to-all of bf16 partial rows back to the
-  token's owner) -> fp32 sum over the destination ranks, one rounding to bf16.
+  route own tokens -> DISPATCH (ONE all-to-all of packed rows: fp8 row + scales + the token's top-k
+  ids/weights, one copy per (token, destination rank); b200moe_ep_pack / _unpack) -> local experts
+  (b200moe_forward_routed: bf16 row = sum over the local experts of a received token) -> COMBINE
+  (all-to-all of the bf16 partial rows back to the token's owner) -> b200moe_ep_combine: fp32 sum over
+  the destination ranks in rank order, one rounding to bf16.
 
 One process per GPU, `torch.distributed` (NCCL over NVLink) for the exchange.  The exchange logic
-is independent of where routing and the expert math run: `route_fn` / `experts_fn` default to the
-CUDA library and can be replaced (the CPU tests run the same exchange over gloo with the oracle
-as the local compute).
+is independent of where the per-rank compute runs: `backend` defaults to the CUDA library
+(`CudaBackend`); the CPU tests run the same exchange over gloo with a backend built on the oracle.
 """
 from __future__ import annotations
 
@@ -61,83 +61,82 @@ def plan_dispatch(topk_idx: torch.Tensor, experts_per_rank: int, world: int, gro
 
 def _a2a(x: torch.Tensor, out_rows: int, in_splits, out_splits, group):
     out = torch.empty((out_rows,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-    if x.dtype == torch.float8_e4m3fn:      # NCCL moves bytes; view fp8 as uint8
-        dist.all_to_all_single(out.view(torch.uint8), x.view(torch.uint8), out_splits, in_splits, group=group)
-    else:
-        dist.all_to_all_single(out, x, out_splits, in_splits, group=group)
+    dist.all_to_all_single(out, x, out_splits, in_splits, group=group)
     return out
 
 
+class CudaBackend:
+    """The per-rank compute of a step on the CUDA library: routing, packing / unpacking of the dispatch
+    rows, the local experts, the owner-side combine.  The CPU tests of the exchange pass an object with
+    the same five methods built on the oracle."""
+
+    def __init__(self, shape: MoEShape, weights: dict, offset: int, device=None):
+        from .main import MoELayer
+        self.layer, self.w, self.offset = MoELayer(shape, device), weights, offset
+
+    def route(self, logits, bias, rsf):
+        return self.layer.route(logits, bias, rsf)
+
+    def pack(self, hidden, hscale, idx, w, send_token):
+        return self.layer.ep_pack(hidden, hscale, idx, w, send_token)
+
+    def unpack(self, wire):
+        return self.layer.ep_unpack(wire)
+
+    def experts(self, idx, w, hidden, hscale):
+        """bf16 [n, H]: per received token the sum over this rank's experts."""
+        return self.layer.forward_routed(idx, w, hidden, hscale, self.w["gemm1_weights"], self.w["gemm1_weights_scale"],
+                                         self.w["gemm2_weights"], self.w["gemm2_weights_scale"], self.offset,
+                                         out_dtype=torch.bfloat16)
+
+    def combine(self, back, row_of, T):
+        return self.layer.ep_combine(back, row_of, T)
+
+
 class ExpertParallelMoE:
-    def __init__(self, shape: MoEShape, weights: dict, group=None, route_fn=None, experts_fn=None, combine_fn=None,
-                 device=None):
+    def __init__(self, shape: MoEShape, weights: dict, group=None, backend=None, device=None):
         """`shape.num_local_experts` experts per rank, rank r owning experts [r*E_local, (r+1)*E_local);
-        `weights` = this rank's gemm1/gemm2 weights and scales.  `route_fn`, `experts_fn` and `combine_fn`
-        default to the CUDA library; the CPU tests of the exchange pass their own."""
-        self.shape, self.group, self.w = shape, group, weights
+        `weights` = this rank's gemm1/gemm2 weights and scales."""
+        self.shape, self.group = shape, group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         if shape.num_local_experts * self.world != shape.num_experts:
             raise ValueError("num_local_experts * world_size must equal num_experts")
         self.offset = self.rank * shape.num_local_experts
-        self._layer = None
-        if route_fn is None or experts_fn is None or combine_fn is None:
-            from .main import MoELayer
-            self._layer = MoELayer(shape, device)
-        self.route_fn = route_fn or self._route_cuda
-        self.experts_fn = experts_fn or self._experts_cuda
-        self.combine_fn = combine_fn or self._combine_cuda
+        self.backend = backend or CudaBackend(shape, weights, self.offset, device)
         self.last_plan = None
-
-    # ---- default local compute: the CUDA library
-    def _route_cuda(self, logits, bias, rsf):
-        return self._layer.route(logits, bias, rsf)
-
-    def _experts_cuda(self, idx, w, hidden, hscale):
-        return self._layer.forward_routed(idx, w, hidden, hscale, self.w["gemm1_weights"],
-                                          self.w["gemm1_weights_scale"], self.w["gemm2_weights"],
-                                          self.w["gemm2_weights_scale"], self.offset, out_dtype=torch.bfloat16)
-
-    def _combine_cuda(self, back, row_of, T):
-        return self._layer.ep_combine(back, row_of, T)
 
     # ---- one step
     @torch.no_grad()
     def forward(self, routing_logits, routing_bias, hidden_states, hidden_states_scale, routed_scaling_factor):
         """Inputs are this rank's tokens (hidden_states_scale is [H/128, T_local]); returns bf16
-        [T_local, H], the full layer output for those tokens."""
-        s, g = self.shape, self.group
+        [T_local, H], the full layer output for those tokens.  Three all-to-alls per step: split sizes,
+        dispatch rows, partial result rows."""
+        s, g, be = self.shape, self.group, self.backend
         T, H = hidden_states.shape
         mark = self._mark
         mark("start")
-        idx, w = self.route_fn(routing_logits, routing_bias, routed_scaling_factor)
+        idx, w = be.route(routing_logits, routing_bias, routed_scaling_factor)
+        idx = idx.to(torch.int32)
         mark("route")
         plan = plan_dispatch(idx, s.num_local_experts, self.world, g)
         self.last_plan = plan
-        tok = plan.send_token
         n_recv = sum(plan.recv_counts)
         mark("plan")
-        # DISPATCH: rows, scales (token-major on the wire), ids and weights of every sent token
-        x_send = hidden_states.view(torch.uint8).index_select(0, tok).view(torch.float8_e4m3fn)
-        sc_send = hidden_states_scale.t().index_select(0, tok).contiguous()
-        idx_send = idx.to(torch.int32).index_select(0, tok)
-        w_send = w.index_select(0, tok)
-        x_recv = _a2a(x_send, n_recv, plan.send_counts, plan.recv_counts, g)
-        sc_recv = _a2a(sc_send, n_recv, plan.send_counts, plan.recv_counts, g)
-        idx_recv = _a2a(idx_send, n_recv, plan.send_counts, plan.recv_counts, g)
-        w_recv = _a2a(w_send, n_recv, plan.send_counts, plan.recv_counts, g)
+        # DISPATCH: one packed row per (token, destination rank)
+        wire = be.pack(hidden_states, hidden_states_scale, idx, w, plan.send_token)
+        wire = _a2a(wire, n_recv, plan.send_counts, plan.recv_counts, g)
+        x_recv, sc_recv, idx_recv, w_recv = be.unpack(wire)
         mark("dispatch")
         # LOCAL EXPERTS: sum over this rank's experts for every received token, as bf16 rows
         if n_recv:
-            part = self.experts_fn(idx_recv, w_recv, x_recv, sc_recv.t().contiguous())
+            part = be.experts(idx_recv, w_recv, x_recv, sc_recv)
         else:
             part = torch.zeros(0, H, dtype=torch.bfloat16, device=hidden_states.device)
-        if part.dtype != torch.bfloat16:
-            part = part.to(torch.bfloat16)
         mark("experts")
         # COMBINE: bf16 partial rows back to the owners, fp32 sum over destination ranks, one rounding
-        back = _a2a(part, tok.numel(), plan.recv_counts, plan.send_counts, g)
-        out = self.combine_fn(back, plan.row_of, T)
+        back = _a2a(part, plan.send_token.numel(), plan.recv_counts, plan.send_counts, g)
+        out = be.combine(back, plan.row_of, T)
         mark("combine")
         return out
 
@@ -163,14 +162,14 @@ class ExpertParallelMoE:
         return {k: v / max(n, 1) for k, v in acc.items()}
 
     def nvlink_bytes(self):
-        """Bytes this rank sent to OTHER ranks in the last step (dispatch + combine partials received
-        count on the peers' side): the figure the NVLink term of the roofline uses."""
+        """Bytes this rank sent to / received from OTHER ranks in the last step: the figure the NVLink
+        term of the roofline uses."""
         p, s = self.last_plan, self.shape
         if p is None:
             return 0
         remote_send = sum(c for d, c in enumerate(p.send_counts) if d != self.rank)
         remote_recv = sum(c for d, c in enumerate(p.recv_counts) if d != self.rank)
-        row = s.hidden + 4 * (s.hidden // 128) + 8 * s.top_k
+        row = (s.hidden + 4 * (s.hidden // 128) + 8 * s.top_k + 15) // 16 * 16
         return {"dispatch_send": remote_send * row, "combine_send": remote_recv * 2 * s.hidden,
                 "dispatch_recv": remote_recv * row, "combine_recv": remote_send * 2 * s.hidden}
 
@@ -246,7 +245,7 @@ def bench(args, spec, name, rank, world, local):
 
     # realised work over all ranks
     n_recv = torch.tensor([sum(ep.last_plan.recv_counts)], device=dev, dtype=torch.float64)
-    idx, _ = ep.route_fn(logits, bias, spec["rsf"])
+    idx, _ = ep.backend.route(logits, bias, spec["rsf"])
     pairs = torch.tensor([float(idx.numel())], device=dev, dtype=torch.float64)
     link = torch.tensor([float(max(nv["dispatch_send"] + nv["combine_send"], nv["dispatch_recv"] + nv["combine_recv"]))],
                         device=dev, dtype=torch.float64)
@@ -265,7 +264,8 @@ def bench(args, spec, name, rank, world, local):
                        "l2": "inputs larger than L2 (%.2f GB of expert weights per rank)" % (w_bytes_rank / 1e9)},
             "e2e": {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-            "gpu_launches": int(ep._layer.launches_per_forward(per)) * K * world if ep._layer else 0,
+            # per rank and step: route, pack, unpack, count, permute, gather, GEMM1, GEMM2, combine, ep_combine
+            "gpu_launches": 10 * K * world,
             "roofline": {"kernel": "whole step, slowest rank", "bound": "hbm", "peak_source": "measured",
                          "achieved": w_bytes_rank / (ms_step * 1e-3) / 1e9, "peak": _hbm_peak(), "unit": "GB/s",
                          "frac": w_bytes_rank / (ms_step * 1e-3) / 1e9 / _hbm_peak(), "traffic": None,

@@ -159,6 +159,37 @@ class MoELayer:
         _lib.check(rc, "b200moe_forward_routed")
         return output
 
+    def ep_row_bytes(self) -> int:
+        n = C.c_int(0)
+        _lib.check(_lib.lib.b200moe_ep_row_bytes(self._h, C.byref(n)), "b200moe_ep_row_bytes")
+        return int(n.value)
+
+    def ep_pack(self, hidden_states, hidden_states_scale, topk_idx, topk_w, send_token):
+        """uint8 [n, ep_row_bytes()]: the dispatch rows of the tokens `send_token` (int64 [n])."""
+        n, T = int(send_token.numel()), int(hidden_states.shape[0])
+        if topk_idx.dtype != torch.int32 or topk_w.dtype != torch.float32 or send_token.dtype != torch.int64:
+            raise ValueError("topk_idx int32, topk_w float32, send_token int64")
+        wire = torch.empty(n, self.ep_row_bytes(), dtype=torch.uint8, device=hidden_states.device)
+        stream = torch.cuda.current_stream(hidden_states.device).cuda_stream
+        rc = _lib.lib.b200moe_ep_pack(self._h, _ptr(_contig(hidden_states)), _ptr(_contig(hidden_states_scale)),
+                                      _ptr(_contig(topk_idx)), _ptr(_contig(topk_w)), _ptr(_contig(send_token)), n, T,
+                                      _ptr(wire), C.c_void_p(stream))
+        _lib.check(rc, "b200moe_ep_pack")
+        return wire
+
+    def ep_unpack(self, wire):
+        """(hidden fp8 [n, H], scales float [H/128, n], topk_idx int32 [n, K], topk_w float [n, K])."""
+        s, n, dev = self.shape, int(wire.shape[0]), wire.device
+        x = torch.empty(n, s.hidden, dtype=torch.float8_e4m3fn, device=dev)
+        sc = torch.empty(s.hidden // 128, n, dtype=torch.float32, device=dev)
+        idx = torch.empty(n, s.top_k, dtype=torch.int32, device=dev)
+        w = torch.empty(n, s.top_k, dtype=torch.float32, device=dev)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = _lib.lib.b200moe_ep_unpack(self._h, _ptr(_contig(wire)), n, _ptr(x), _ptr(sc), _ptr(idx), _ptr(w),
+                                        C.c_void_p(stream))
+        _lib.check(rc, "b200moe_ep_unpack")
+        return x, sc, idx, w
+
     def ep_combine(self, partial_rows, row_of, num_tokens):
         """Owner-rank side of the expert-parallel combine: bf16 [T, hidden] = per token the fp32 sum, in
         rank order, of the bf16 rows `partial_rows[row_of[r, t]]` (row_of int32 [world, T], -1 = none)."""

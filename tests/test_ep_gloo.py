@@ -36,25 +36,46 @@ def _worker(rank, world, port, out_q):
         sl = slice(rank * per, (rank + 1) * per)
         weights = I.make_weights(shape, 9, "cpu", rank * shape.num_local_experts, std=STD)
 
-        def route_fn(logits, bias, rsf):
-            idx, w = O.route_ds(logits, bias, shape.top_k, shape.n_group, shape.topk_group, rsf)
-            return idx.to(torch.int32), w
+        class OracleBackend:
+            """The five per-rank steps on the CPU: the oracle for routing and experts, plain torch
+            restatements of the pack / unpack / combine kernels (same wire format)."""
+            KB = shape.hidden // 128
 
-        def experts_fn(idx, w, hidden, hscale):
-            out, _, _ = O.run_experts(hidden, hscale, weights["gemm1_weights"], weights["gemm1_weights_scale"],
-                                      weights["gemm2_weights"], weights["gemm2_weights_scale"], w, idx.long(),
-                                      rank * shape.num_local_experts, shape.num_experts)
-            return out
+            def route(self, logits, bias, rsf):
+                idx, w = O.route_ds(logits, bias, shape.top_k, shape.n_group, shape.topk_group, rsf)
+                return idx.to(torch.int32), w
 
-        def combine_fn(back, row_of, T):
-            # restatement of b200moe_ep_combine: fp32 sum in rank order, one rounding
-            acc = torch.zeros(T, back.shape[1], dtype=torch.float32)
-            for r in range(row_of.shape[0]):
-                has = row_of[r] >= 0
-                acc[has] += back[row_of[r][has].long()].float()
-            return acc.to(torch.bfloat16)
+            def pack(self, hidden, hscale, idx, w, send_token):
+                rows = [hidden.view(torch.uint8)[send_token],
+                        hscale.t()[send_token].contiguous().view(torch.uint8).reshape(len(send_token), -1),
+                        idx[send_token].contiguous().view(torch.uint8).reshape(len(send_token), -1),
+                        w[send_token].contiguous().view(torch.uint8).reshape(len(send_token), -1)]
+                wire = torch.cat(rows, dim=1)
+                pad = (-wire.shape[1]) % 16
+                return torch.nn.functional.pad(wire, (0, pad)).contiguous()
 
-        ep = ExpertParallelMoE(shape, weights, route_fn=route_fn, experts_fn=experts_fn, combine_fn=combine_fn)
+            def unpack(self, wire):
+                H, K, KB = shape.hidden, shape.top_k, self.KB
+                x = wire[:, :H].contiguous().view(torch.float8_e4m3fn)
+                sc = wire[:, H:H + 4 * KB].contiguous().view(torch.float32).t().contiguous()
+                idx = wire[:, H + 4 * KB:H + 4 * KB + 4 * K].contiguous().view(torch.int32)
+                w = wire[:, H + 4 * KB + 4 * K:H + 4 * KB + 8 * K].contiguous().view(torch.float32)
+                return x, sc, idx, w
+
+            def experts(self, idx, w, hidden, hscale):
+                out, _, _ = O.run_experts(hidden, hscale, weights["gemm1_weights"], weights["gemm1_weights_scale"],
+                                          weights["gemm2_weights"], weights["gemm2_weights_scale"], w, idx.long(),
+                                          rank * shape.num_local_experts, shape.num_experts)
+                return out.to(torch.bfloat16)
+
+            def combine(self, back, row_of, T):
+                acc = torch.zeros(T, back.shape[1], dtype=torch.float32)     # fp32 sum in rank order, one rounding
+                for r in range(row_of.shape[0]):
+                    has = row_of[r] >= 0
+                    acc[has] += back[row_of[r][has].long()].float()
+                return acc.to(torch.bfloat16)
+
+        ep = ExpertParallelMoE(shape, weights, backend=OracleBackend())
         out = ep.forward(tokens["routing_logits"][sl], tokens["routing_bias"],
                          tokens["hidden_states"].view(torch.uint8)[sl].view(torch.float8_e4m3fn),
                          tokens["hidden_states_scale"][:, sl].contiguous(), RSF)

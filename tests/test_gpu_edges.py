@@ -138,3 +138,24 @@ def test_forward_routed_bf16_is_the_rounded_fp32_result():
     b16 = layer.forward_routed(*args, out_dtype=torch.bfloat16)
     torch.cuda.synchronize()
     assert torch.equal(b16.view(torch.int16), f32.to(torch.bfloat16).view(torch.int16))
+
+
+def test_ep_pack_unpack_round_trip():
+    """b200moe_ep_pack / _unpack: the wire row is [fp8 row | scales | ids | weights] padded to 16 bytes;
+    unpacking returns the operator's layouts (scales K-block major) for exactly the packed tokens."""
+    from justgoal_b200 import MoELayer
+    shape = I.TINY_DS
+    T = 50
+    d = util.to_cuda(I.make_inputs(shape, T, seed=63))
+    layer = MoELayer(shape)
+    idx, w = layer.route(d["routing_logits"], d["routing_bias"], d["routed_scaling_factor"])
+    send = torch.tensor([3, 3, 49, 0, 17, 20, 21, 48], dtype=torch.int64, device="cuda")
+    wire = layer.ep_pack(d["hidden_states"], d["hidden_states_scale"], idx, w, send)
+    H, K, KB = shape.hidden, shape.top_k, shape.hidden // 128
+    assert wire.shape == (send.numel(), (H + 4 * KB + 8 * K + 15) // 16 * 16) == (send.numel(), layer.ep_row_bytes())
+    assert torch.equal(wire[:, :H], d["hidden_states"].view(torch.uint8)[send])
+    x, sc, i2, w2 = layer.ep_unpack(wire)
+    torch.cuda.synchronize()
+    assert torch.equal(x.view(torch.uint8), d["hidden_states"].view(torch.uint8)[send])
+    assert torch.equal(sc, d["hidden_states_scale"][:, send])
+    assert torch.equal(i2, idx[send]) and torch.equal(w2, w[send])
