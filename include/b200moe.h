@@ -151,6 +151,37 @@ int b200moe_ep_pack(b200moe_handle h, const void* hidden_states, const void* hid
 int b200moe_ep_unpack(b200moe_handle h, const void* wire, int n_rows, void* hidden_states,
                       void* hidden_states_scale, int32_t* topk_idx, float* topk_w, void* cuda_stream);
 
+/* The same exchange over peer memory (NVLink) instead of a library all-to-all.  Every rank owns one
+ * buffer that all ranks of the node have mapped (how it is shared - symmetric memory, CUDA IPC - is
+ * the host's business; this library only receives the peer addresses):
+ *   flags uint32[16], zero before the first step; wire [world][cap] dispatch rows; back [world][cap][H] bf16.
+ * A step on every rank, all launches on one stream, `cap` the same on all ranks, T <= cap:
+ *   b200moe_ep_push          own tokens' rows stored into wire slot (my_rank, t) of every rank that owns
+ *                            one of the token's experts; the slot of every other rank gets expert ids -1
+ *   b200moe_ep_barrier       epoch e (strictly increasing over the life of the buffers)
+ *   b200moe_ep_unpack_slots  my wire, all world*cap slots -> inputs of b200moe_forward_routed
+ *   b200moe_forward_routed   over world*cap tokens, bf16 rows out
+ *   b200moe_ep_return        result rows of present slots stored into back slot (my_rank, t) of the owner
+ *   b200moe_ep_barrier       epoch e + 1
+ *   b200moe_ep_combine_slots out[t] = fp32 sum, in rank order, of my back slots (r, t) over the ranks r
+ *                            that own one of token t's experts; one rounding to bf16
+ * peer_* are host arrays of `world` device addresses (entry r = the buffer part on rank r).
+ * The barrier's wait gives up after 2 s and then stores 7 into *status_word (a device int the
+ * caller owns and zeroes); the step's output is invalid in that case.  Only plain stores cross
+ * NVLink.  (No counterpart in the reference.) */
+int b200moe_ep_push(b200moe_handle h, const void* hidden_states, const void* hidden_states_scale,
+                    const int32_t* topk_idx, const float* topk_w, int num_tokens, int cap, int world,
+                    int my_rank, void* const* peer_wire, void* cuda_stream);
+int b200moe_ep_barrier(b200moe_handle h, void* const* peer_flags, int world, int my_rank,
+                       unsigned epoch, int* status_word, void* cuda_stream);
+int b200moe_ep_unpack_slots(b200moe_handle h, const void* wire, int n_slots, void* hidden_states,
+                            void* hidden_states_scale, int32_t* topk_idx, float* topk_w,
+                            void* cuda_stream);
+int b200moe_ep_return(b200moe_handle h, const void* partial_rows_bf16, const int32_t* topk_idx_slots,
+                      int cap, int world, int my_rank, void* const* peer_back, void* cuda_stream);
+int b200moe_ep_combine_slots(b200moe_handle h, const void* back, const int32_t* topk_idx,
+                             int num_tokens, int cap, int world, void* output_bf16, void* cuda_stream);
+
 /* Expert-parallel combine on the token's owner rank: out[t, :] = sum over the ranks r that
  * computed a share of token t (row_of[r, t] >= 0) of partial_rows[row_of[r, t], :], added in
  * fp32 in ascending rank order, rounded once to bf16.  partial_rows is the receive buffer

@@ -17,6 +17,7 @@
 #include "../../include/b200moe.h"
 #include "common.cuh"
 #include "front.cuh"
+#include "ep_p2p.cuh"
 #include "gemm.cuh"
 #include "permute.cuh"
 #include "routing.cuh"
@@ -557,6 +558,83 @@ int b200moe_ep_unpack(b200moe_handle h, const void* wire, int n_rows, void* hidd
     ep_unpack_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint8_t*>(wire), n_rows, h->cfg.hidden, h->cfg.top_k, static_cast<uint8_t*>(hidden),
         static_cast<float*>(hidden_scale), topk_idx, topk_w);
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
+// ---- exchange over peer memory (ep_p2p.cuh)
+static bool fill_peers(PeerPtrs& pp, void* const* peers, int world) {
+    if (!peers || world < 1 || world > EP_P2P_MAX_WORLD) return false;
+    for (int r = 0; r < EP_P2P_MAX_WORLD; ++r) pp.p[r] = r < world ? peers[r] : nullptr;
+    for (int r = 0; r < world; ++r) if (!pp.p[r]) return false;
+    return true;
+}
+static int row_grid(b200moe_ctx* h, long long rows) {
+    long long g = (rows + 7) / 8;
+    if (g > (long long)h->num_sms * 8) g = (long long)h->num_sms * 8;
+    return g < 1 ? 1 : (int)g;
+}
+
+int b200moe_ep_push(b200moe_handle h, const void* hidden, const void* hidden_scale, const int32_t* topk_idx,
+                    const float* topk_w, int T, int cap, int world, int my_rank, void* const* peer_wire, void* stream) {
+    PeerPtrs pp;
+    if (!h || T < 0 || cap < 1 || T > cap || my_rank < 0 || my_rank >= world || h->cfg.top_k > 32 ||
+        !fill_peers(pp, peer_wire, world) || h->cfg.num_local_experts * world != h->cfg.num_experts)
+        return B200MOE_E_BADARG;
+    if (T > 0 && (!hidden || !hidden_scale || !topk_idx || !topk_w)) return B200MOE_E_BADARG;
+    ep_push_kernel<<<row_grid(h, cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(hidden), static_cast<const float*>(hidden_scale), topk_idx, topk_w, T, cap,
+        h->cfg.hidden, h->cfg.top_k, h->cfg.num_local_experts, world, my_rank, pp);
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
+int b200moe_ep_barrier(b200moe_handle h, void* const* peer_flags, int world, int my_rank, unsigned epoch,
+                       int* status_word, void* stream) {
+    PeerPtrs pp;
+    if (!h || my_rank < 0 || my_rank >= world || !status_word || !fill_peers(pp, peer_flags, world))
+        return B200MOE_E_BADARG;
+    ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, my_rank, epoch, status_word);
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
+int b200moe_ep_unpack_slots(b200moe_handle h, const void* wire, int n_slots, void* hidden, void* hidden_scale,
+                            int32_t* topk_idx, float* topk_w, void* stream) {
+    if (!h || n_slots < 0 || h->cfg.top_k > 32) return B200MOE_E_BADARG;
+    if (n_slots == 0) return 0;
+    if (!wire || !hidden || !hidden_scale || !topk_idx || !topk_w) return B200MOE_E_BADARG;
+    ep_unpack_slots_kernel<<<row_grid(h, n_slots), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(wire), n_slots, h->cfg.hidden, h->cfg.top_k, static_cast<uint8_t*>(hidden),
+        static_cast<float*>(hidden_scale), topk_idx, topk_w);
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
+int b200moe_ep_return(b200moe_handle h, const void* partial_rows, const int32_t* topk_idx_slots, int cap, int world,
+                      int my_rank, void* const* peer_back, void* stream) {
+    PeerPtrs pp;
+    if (!h || cap < 1 || my_rank < 0 || my_rank >= world || !partial_rows || !topk_idx_slots ||
+        !fill_peers(pp, peer_back, world) || h->cfg.hidden % 8)
+        return B200MOE_E_BADARG;
+    ep_return_kernel<<<row_grid(h, (long long)world * cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(partial_rows), topk_idx_slots, cap, h->cfg.hidden, h->cfg.top_k, world,
+        my_rank, pp);
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
+int b200moe_ep_combine_slots(b200moe_handle h, const void* back, const int32_t* topk_idx, int T, int cap, int world,
+                             void* output_bf16, void* stream) {
+    if (!h || T < 0 || cap < 1 || T > cap || world < 1 || world > EP_P2P_MAX_WORLD || h->cfg.hidden % 8 ||
+        h->cfg.num_local_experts * world != h->cfg.num_experts)
+        return B200MOE_E_BADARG;
+    if (T == 0) return 0;
+    if (!back || !topk_idx || !output_bf16) return B200MOE_E_BADARG;
+    const int grid = T < h->num_sms * 8 ? T : h->num_sms * 8;
+    ep_combine_slots_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(back), topk_idx, T, cap, h->cfg.hidden, h->cfg.top_k,
+        h->cfg.num_local_experts, world, static_cast<__nv_bfloat16*>(output_bf16));
     CU_TRY(cudaGetLastError());
     return 0;
 }

@@ -93,8 +93,96 @@ class CudaBackend:
         return self.layer.ep_combine(back, row_of, T)
 
 
+class PeerExchange:
+    """The exchange over peer memory (NVLink stores + flag barriers, csrc/ep_p2p.cuh) instead of NCCL
+    all-to-alls: no host synchronisation and no library collective in a step.  One symmetric buffer per
+    rank (torch symmetric memory supplies the mapping and the peer addresses; the kernels are this
+    library's): flags | status word | wire [world][cap] rows | back [world][cap][H] bf16."""
+
+    FLAGS_BYTES = 4096          # flags uint32[16] at 0, device status int at 1024
+
+    def __init__(self, layer, shape: MoEShape, cap: int, group, device):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm
+        from . import _lib
+        self._lib, self._C = _lib, C
+        self.layer, self.shape, self.cap = layer, shape, int(cap)
+        device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.row_bytes = layer.ep_row_bytes()
+        wire_bytes = self.world * self.cap * self.row_bytes
+        back_bytes = self.world * self.cap * shape.hidden * 2
+        self.wire_off = self.FLAGS_BYTES
+        self.back_off = (self.wire_off + wire_bytes + 255) // 256 * 256
+        total = self.back_off + back_bytes
+        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+        bases = [int(p) for p in self.handle.buffer_ptrs]
+        arr = C.c_void_p * self.world
+        self.peer_flags = arr(*bases)
+        self.peer_wire = arr(*[b + self.wire_off for b in bases])
+        self.peer_back = arr(*[b + self.back_off for b in bases])
+        self.status = self.buf[1024:1028].view(torch.int32)
+        self.wire = self.buf[self.wire_off:self.wire_off + wire_bytes].view(self.world * self.cap, self.row_bytes)
+        self.back = self.buf[self.back_off:self.back_off + back_bytes].view(torch.bfloat16).view(
+            self.world * self.cap, shape.hidden)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)           # every rank's flags are zero before anyone's first barrier kernel
+
+    def _stream(self):
+        return self._C.c_void_p(torch.cuda.current_stream(self.buf.device).cuda_stream)
+
+    def _check(self, rc, what):
+        self._lib.check(rc, what)
+
+    def barrier(self):
+        self.epoch += 1
+        self._check(self._lib.lib.b200moe_ep_barrier(self.layer._h, self.peer_flags, self.world, self.rank, self.epoch,
+                                                     self.status.data_ptr(), self._stream()), "b200moe_ep_barrier")
+
+    def push(self, hidden, hscale, idx, w):
+        T = int(hidden.shape[0])
+        if T > self.cap:
+            raise ValueError(f"{T} tokens exceed the exchange capacity {self.cap}")
+        self._keep = (hidden.contiguous(), hscale.contiguous(), idx.contiguous(), w.contiguous())
+        h, sc, i, ww = self._keep
+        self._check(self._lib.lib.b200moe_ep_push(self.layer._h, h.data_ptr(), sc.data_ptr(), i.data_ptr(), ww.data_ptr(),
+                                                  T, self.cap, self.world, self.rank, self.peer_wire, self._stream()),
+                    "b200moe_ep_push")
+
+    def unpack(self):
+        s, n, dev = self.shape, self.world * self.cap, self.buf.device
+        x = torch.empty(n, s.hidden, dtype=torch.float8_e4m3fn, device=dev)
+        sc = torch.empty(s.hidden // 128, n, dtype=torch.float32, device=dev)
+        idx = torch.empty(n, s.top_k, dtype=torch.int32, device=dev)
+        w = torch.empty(n, s.top_k, dtype=torch.float32, device=dev)
+        self._check(self._lib.lib.b200moe_ep_unpack_slots(self.layer._h, self.wire.data_ptr(), n, x.data_ptr(),
+                                                          sc.data_ptr(), idx.data_ptr(), w.data_ptr(), self._stream()),
+                    "b200moe_ep_unpack_slots")
+        return x, sc, idx, w
+
+    def give_back(self, part, idx_slots):
+        self._check(self._lib.lib.b200moe_ep_return(self.layer._h, part.data_ptr(), idx_slots.data_ptr(), self.cap,
+                                                    self.world, self.rank, self.peer_back, self._stream()),
+                    "b200moe_ep_return")
+
+    def combine(self, idx, T):
+        out = torch.empty(T, self.shape.hidden, dtype=torch.bfloat16, device=self.buf.device)
+        self._check(self._lib.lib.b200moe_ep_combine_slots(self.layer._h, self.back.data_ptr(), idx.data_ptr(), T, self.cap,
+                                                           self.world, out.data_ptr(), self._stream()),
+                    "b200moe_ep_combine_slots")
+        return out
+
+    def error_word(self) -> int:
+        """Device status of the barriers (0 = fine, 7 = a wait for a peer ran out).  Synchronises."""
+        return int(self.status.item())
+
+
 class ExpertParallelMoE:
-    def __init__(self, shape: MoEShape, weights: dict, group=None, backend=None, device=None):
+    def __init__(self, shape: MoEShape, weights: dict, group=None, backend=None, device=None, exchange="nccl",
+                 capacity=None):
         """`shape.num_local_experts` experts per rank, rank r owning experts [r*E_local, (r+1)*E_local);
         `weights` = this rank's gemm1/gemm2 weights and scales."""
         self.shape, self.group = shape, group
@@ -105,6 +193,15 @@ class ExpertParallelMoE:
         self.offset = self.rank * shape.num_local_experts
         self.backend = backend or CudaBackend(shape, weights, self.offset, device)
         self.last_plan = None
+        # exchange = "nccl": three all-to-alls per step (works with any backend, CPU tests included);
+        # "p2p": this library's kernels over peer memory, `capacity` = the most tokens a rank brings to a step
+        self.peer = None
+        if exchange == "p2p":
+            if backend is not None or capacity is None:
+                raise ValueError("the peer-memory exchange needs the CUDA backend and a capacity")
+            self.peer = PeerExchange(self.backend.layer, shape, capacity, group, device)
+        elif exchange != "nccl":
+            raise ValueError("exchange must be 'nccl' or 'p2p'")
 
     # ---- one step
     @torch.no_grad()
@@ -116,6 +213,21 @@ class ExpertParallelMoE:
         T, H = hidden_states.shape
         mark = self._mark
         mark("start")
+        if self.peer is not None:
+            px = self.peer
+            idx, w = be.route(routing_logits, routing_bias, routed_scaling_factor)
+            mark("route")
+            px.push(hidden_states, hidden_states_scale, idx, w)
+            px.barrier()
+            x_recv, sc_recv, idx_recv, w_recv = px.unpack()
+            mark("dispatch")
+            part = be.experts(idx_recv, w_recv, x_recv, sc_recv)
+            mark("experts")
+            px.give_back(part, idx_recv)
+            px.barrier()
+            out = px.combine(idx, T)
+            mark("combine")
+            return out
         idx, w = be.route(routing_logits, routing_bias, routed_scaling_factor)
         idx = idx.to(torch.int32)
         mark("route")
@@ -166,7 +278,7 @@ class ExpertParallelMoE:
         term of the roofline uses."""
         p, s = self.last_plan, self.shape
         if p is None:
-            return 0
+            return None
         remote_send = sum(c for d, c in enumerate(p.send_counts) if d != self.rank)
         remote_recv = sum(c for d, c in enumerate(p.recv_counts) if d != self.rank)
         row = (s.hidden + 4 * (s.hidden // 128) + 8 * s.top_k + 15) // 16 * 16
@@ -195,7 +307,28 @@ def bench(args, spec, name, rank, world, local):
     hidden = tokens["hidden_states"].view(torch.uint8)[sl].contiguous().view(torch.float8_e4m3fn)
     hscale = tokens["hidden_states_scale"][:, sl].contiguous()
     weights = I.make_weights(shape, 0, dev, rank * shape.num_local_experts)
-    ep = ExpertParallelMoE(shape, weights, device=dev)
+    # Exchange: this library's kernels over peer memory when the node can map it and one step of it agrees
+    # with the NCCL form on the real inputs; else the NCCL form (B200MOE_EP_EXCHANGE=nccl|p2p forces one).
+    import os
+    want = os.environ.get("B200MOE_EP_EXCHANGE", "auto")
+    ep_nccl = ExpertParallelMoE(shape, weights, device=dev)
+    ep, exchange, why = ep_nccl, "nccl", "forced" if want == "nccl" else ""
+    if want != "nccl":
+        ok = torch.ones(1, device=dev)
+        try:
+            ep_p2p = ExpertParallelMoE(shape, weights, device=dev, exchange="p2p", capacity=per)
+            a = ep_nccl.forward(logits, bias, hidden, hscale, spec["rsf"])
+            b = ep_p2p.forward(logits, bias, hidden, hscale, spec["rsf"])
+            torch.cuda.synchronize()
+            if ep_p2p.peer.error_word() != 0 or not torch.allclose(a.float(), b.float(), atol=1e-2, rtol=1e-2):
+                ok.zero_(); why = "peer-memory step differs from the NCCL step"
+        except Exception as e:           # noqa: BLE001 - any failure to set the mapping up means: use NCCL
+            ok.zero_(); why = f"peer-memory setup failed: {type(e).__name__}"
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if float(ok) > 0:
+            ep, exchange = ep_p2p, "p2p"
+        elif want == "p2p":
+            raise SystemExit(f"B200MOE_EP_EXCHANGE=p2p but {why or 'another rank failed'}")
     K, W = args.steps, max(args.warmup, 3)
 
     def sync_time(fn, steps):
@@ -220,6 +353,9 @@ def bench(args, spec, name, rank, world, local):
 
     sync_time(step, 2)           # untimed: first use of the barrier / all-reduce / event path itself
     ms_step = sync_time(step, K)
+    if ep.peer is not None and ep.peer.error_word() != 0:
+        raise SystemExit(f"device error word {ep.peer.error_word()} in the peer-memory exchange")
+    ep.last_plan = plan_dispatch(ep.backend.route(logits, bias, spec["rsf"])[0], shape.num_local_experts, world)
     nv = ep.nvlink_bytes()
     phases = None
     if torch.cuda.is_available():
@@ -260,12 +396,15 @@ def bench(args, spec, name, rank, world, local):
             "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 (block-scaled), bf16 out", "data": "synthetic",
             "config": {"workload": f"{name}: T={T} per step over {world} ranks, hidden {H}, intermediate {Iz}, "
                                    f"{shape.num_local_experts} of {shape.num_experts} experts per rank, top-{shape.top_k}, "
-                                   "expert parallel (NCCL all-to-all dispatch/combine)",
+                                   + ("expert parallel (dispatch/combine by this library's kernels over peer memory)"
+                                      if exchange == "p2p" else "expert parallel (NCCL all-to-all dispatch/combine)"),
+                       "exchange": exchange, "exchange_note": why,
                        "l2": "inputs larger than L2 (%.2f GB of expert weights per rank)" % (w_bytes_rank / 1e9)},
             "e2e": {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-            # per rank and step: route, pack, unpack, count, permute, gather, GEMM1, GEMM2, combine, ep_combine
-            "gpu_launches": 10 * K * world,
+            # per rank and step: route, pack | push + barrier, unpack, count, permute, gather, GEMM1, GEMM2, combine,
+            # [return + barrier,] owner-side combine
+            "gpu_launches": (13 if exchange == "p2p" else 10) * K * world,
             "roofline": {"kernel": "whole step, slowest rank", "bound": "hbm", "peak_source": "measured",
                          "achieved": w_bytes_rank / (ms_step * 1e-3) / 1e9, "peak": _hbm_peak(), "unit": "GB/s",
                          "frac": w_bytes_rank / (ms_step * 1e-3) / 1e9 / _hbm_peak(), "traffic": None,

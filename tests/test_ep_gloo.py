@@ -93,7 +93,7 @@ def test_two_ranks_reproduce_the_single_process_layer():
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    results = sorted([q.get(timeout=240) for _ in range(world)], key=lambda r: r[0])
+    results = sorted(util.collect(q, procs, world, 240), key=lambda r: r[0])
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0

@@ -18,7 +18,7 @@ SHAPE_ALL = I.MoEShape(hidden=512, intermediate=256, num_experts=64, num_local_e
 T_TOTAL, RSF, STD = 300, 2.5, 0.05
 
 
-def _worker(rank, world, port, out_q):
+def _worker(rank, world, port, out_q, exchange):
     import torch.distributed as dist
     sys.path.insert(0, util.ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -31,28 +31,36 @@ def _worker(rank, world, port, out_q):
         per = T_TOTAL // world
         sl = slice(rank * per, (rank + 1) * per)
         weights = {k: v.cuda() for k, v in I.make_weights(shape, 9, "cpu", rank * shape.num_local_experts, std=STD).items()}
-        ep = ExpertParallelMoE(shape, weights)
+        ep = ExpertParallelMoE(shape, weights, exchange=exchange, capacity=per if exchange == "p2p" else None)
         out = ep.forward(tokens["routing_logits"][sl].cuda(), tokens["routing_bias"].cuda(),
                          tokens["hidden_states"].view(torch.uint8)[sl].cuda().view(torch.float8_e4m3fn),
                          tokens["hidden_states_scale"][:, sl].contiguous().cuda(), RSF)
         torch.cuda.synchronize()
+        if ep.peer is not None:
+            # a second step on the same buffers (slots are reused, epochs grow), then the barriers' status
+            out = ep.forward(tokens["routing_logits"][sl].cuda(), tokens["routing_bias"].cuda(),
+                             tokens["hidden_states"].view(torch.uint8)[sl].cuda().view(torch.float8_e4m3fn),
+                             tokens["hidden_states_scale"][:, sl].contiguous().cuda(), RSF)
+            torch.cuda.synchronize()
+            assert ep.peer.error_word() == 0
         out_q.put((rank, out.float().cpu().numpy()))
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpu_expert_parallel_matches_oracle():
+@pytest.mark.parametrize("exchange", ["nccl", "p2p"])
+def test_two_gpu_expert_parallel_matches_oracle(exchange):
     import torch.multiprocessing as mp
     world = 2
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q, exchange)) for r in range(world)]
     for p in procs:
         p.start()
-    results = sorted([q.get(timeout=300) for _ in range(world)], key=lambda r: r[0])
+    results = sorted(util.collect(q, procs, world, 240), key=lambda r: r[0])
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0

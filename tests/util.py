@@ -63,3 +63,21 @@ def routing_margin_ulp(shape, logits, bias):
     srt = torch.sort(v, dim=1, descending=True).values
     gaps = ulp_diff(srt[:, :-1].clamp_min(1e-30), srt[:, 1:].clamp_min(1e-30))
     return gaps.min(dim=1).values
+
+
+def collect(q, procs, n, seconds):
+    """n results from the workers' queue; fails at once when a worker has died instead of waiting out
+    the whole time limit."""
+    import queue
+    import time
+    out, deadline = [], time.time() + seconds
+    while len(out) < n:
+        try:
+            out.append(q.get(timeout=1.0))
+        except queue.Empty:
+            dead = [p.exitcode for p in procs if p.exitcode not in (None, 0)]
+            if dead:
+                raise AssertionError(f"worker exited with {dead} before reporting")
+            if time.time() > deadline:
+                raise AssertionError("workers did not report in time")
+    return out
