@@ -1,14 +1,15 @@
 """B200-native FP8 block-scale MoE layer behind the reference's operator entry point.
 
 `run` / `run_dps` keep the reference solutions' `main.py::run` signature; `MoELayer` is the
-handle-based form for other shapes (e.g. the Qwen3-MoE shape) and for expert parallelism.
+handle-based form for other shapes (e.g. the Qwen3-MoE shape) and for expert parallelism;
+`HostPipeline` overlaps the host<->device copies of consecutive steps with the forward.
 They are resolved on first use, which loads libb200moe.so and raises if it is missing (build
 it with `python -m justgoal_b200.build`): there is no CPU or PyTorch fallback.
 """
 from .inputs import (DEEPSEEK_V3, QWEN3_MOE, TINY_DS, TINY_RENORM, MoEShape, ROUTING_DS,  # noqa: F401
                      ROUTING_RENORM_NAIVE)
 
-_LAZY = {"MoELayer": "main", "run": "main", "run_dps": "main", "B200MoEError": "_lib"}
+_LAZY = {"MoELayer": "main", "HostPipeline": "main", "run": "main", "run_dps": "main", "B200MoEError": "_lib"}
 
 
 def __getattr__(name):

@@ -265,6 +265,62 @@ def _layer_for(routing_logits, hidden_states, gemm1_weights, top_k=8, n_group=8,
     return layer
 
 
+class HostPipeline:
+    """Steady-state loop for callers whose per-step inputs live in pinned host memory: the copy in, the
+    forward and the copy out run on three streams over `depth` sets of device buffers, so step i+1's
+    inputs travel while step i computes and step i-1's output travels back.  Every step still copies its
+    own inputs to the device and its own output to the host; only the overlap is added.
+
+        pipe = HostPipeline(layer, T, routing_bias, weights..., local_expert_offset, routed_scaling_factor)
+        for logits, hidden, scale, out in steps:      # pinned host tensors
+            pipe.step(logits, hidden, scale, out)
+        pipe.drain()                                  # all outputs have landed
+    """
+
+    def __init__(self, layer: "MoELayer", num_tokens, routing_bias, gemm1_weights, gemm1_weights_scale,
+                 gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, depth=2):
+        s, dev, T = layer.shape, layer.device, int(num_tokens)
+        self.layer, self.T, self.depth, self.n = layer, T, int(depth), 0
+        self.static = (routing_bias, gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
+                       local_expert_offset, routed_scaling_factor)
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+        mk = lambda *shape, dtype: torch.empty(*shape, dtype=dtype, device=dev)   # noqa: E731
+        self.slots = [dict(logits=mk(T, s.num_experts, dtype=torch.float32),
+                           hidden=mk(T, s.hidden, dtype=torch.float8_e4m3fn),
+                           scale=mk(s.hidden // 128, T, dtype=torch.float32),
+                           out=mk(T, s.hidden, dtype=torch.bfloat16),
+                           loaded=torch.cuda.Event(), computed=torch.cuda.Event(), stored=torch.cuda.Event())
+                      for _ in range(self.depth)]
+
+    @torch.no_grad()
+    def step(self, host_logits, host_hidden, host_scale, host_out):
+        b = self.slots[self.n % self.depth]
+        reuse = self.n >= self.depth
+        bias, w13, s13, w2, s2, off, rsf = self.static
+        with torch.cuda.stream(self.s_in):
+            if reuse:
+                self.s_in.wait_event(b["computed"])      # the forward that read this slot's inputs is done
+            b["logits"].copy_(host_logits, non_blocking=True)
+            b["hidden"].view(torch.uint8).copy_(host_hidden.view(torch.uint8), non_blocking=True)
+            b["scale"].copy_(host_scale, non_blocking=True)
+            b["loaded"].record()
+        with torch.cuda.stream(self.s_run):
+            self.s_run.wait_event(b["loaded"])
+            if reuse:
+                self.s_run.wait_event(b["stored"])       # this slot's previous output has left the device
+            self.layer.forward(b["logits"], bias, b["hidden"], b["scale"], w13, s13, w2, s2, off, rsf, output=b["out"])
+            b["computed"].record()
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(b["computed"])
+            host_out.copy_(b["out"], non_blocking=True)
+            b["stored"].record()
+        self.n += 1
+
+    def drain(self):
+        for st in (self.s_in, self.s_run, self.s_out):
+            st.synchronize()
+
+
 @torch.no_grad()
 def run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
         gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor):

@@ -159,3 +159,28 @@ def test_ep_pack_unpack_round_trip():
     assert torch.equal(x.view(torch.uint8), d["hidden_states"].view(torch.uint8)[send])
     assert torch.equal(sc, d["hidden_states_scale"][:, send])
     assert torch.equal(i2, idx[send]) and torch.equal(w2, w[send])
+
+
+def test_host_pipeline_returns_every_steps_own_result():
+    """HostPipeline overlaps copies and forwards of consecutive steps over two sets of device buffers:
+    each step's host output must be that step's own result, bit for bit."""
+    from justgoal_b200 import HostPipeline, MoELayer
+    shape, T = I.TINY_DS, 40
+    layer = MoELayer(shape)
+    base = util.to_cuda(I.make_inputs(shape, T, seed=70))
+    static = [base[k] for k in ("routing_bias", "gemm1_weights", "gemm1_weights_scale", "gemm2_weights",
+                                "gemm2_weights_scale", "local_expert_offset", "routed_scaling_factor")]
+    steps = []
+    for i in range(5):
+        tok = I.make_tokens(shape, T, seed=71 + i, device="cpu")
+        steps.append(dict(logits=tok["routing_logits"].pin_memory(), hidden=tok["hidden_states"].pin_memory(),
+                          scale=tok["hidden_states_scale"].pin_memory(),
+                          out=torch.empty(T, shape.hidden, dtype=torch.bfloat16).pin_memory()))
+    pipe = HostPipeline(layer, T, *static)
+    for s in steps:
+        pipe.step(s["logits"], s["hidden"], s["scale"], s["out"])
+    pipe.drain()
+    for s in steps:
+        want = layer.forward(s["logits"].cuda(), static[0], s["hidden"].cuda(), s["scale"].cuda(), *static[1:])
+        torch.cuda.synchronize()
+        assert torch.equal(s["out"].view(torch.int16), want.cpu().view(torch.int16))
