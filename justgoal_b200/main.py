@@ -278,9 +278,13 @@ class HostPipeline:
     """
 
     def __init__(self, layer: "MoELayer", num_tokens, routing_bias, gemm1_weights, gemm1_weights_scale,
-                 gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, depth=2):
+                 gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, depth=2,
+                 forward_fn=None):
+        """`forward_fn(logits, hidden, scale, out) -> tensor` replaces `layer.forward` (the expert-parallel
+        layer passes its own step); it runs on the pipeline's compute stream."""
         s, dev, T = layer.shape, layer.device, int(num_tokens)
         self.layer, self.T, self.depth, self.n = layer, T, int(depth), 0
+        self.forward_fn = forward_fn
         self.static = (routing_bias, gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
                        local_expert_offset, routed_scaling_factor)
         self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
@@ -308,11 +312,17 @@ class HostPipeline:
             self.s_run.wait_event(b["loaded"])
             if reuse:
                 self.s_run.wait_event(b["stored"])       # this slot's previous output has left the device
-            self.layer.forward(b["logits"], bias, b["hidden"], b["scale"], w13, s13, w2, s2, off, rsf, output=b["out"])
+            if self.forward_fn is None:
+                o = self.layer.forward(b["logits"], bias, b["hidden"], b["scale"], w13, s13, w2, s2, off, rsf,
+                                       output=b["out"])
+            else:
+                o = self.forward_fn(b["logits"], b["hidden"], b["scale"], b["out"])
+                if o.data_ptr() != b["out"].data_ptr():
+                    o.record_stream(self.s_out)          # allocated on the compute stream, read on the copy stream
             b["computed"].record()
         with torch.cuda.stream(self.s_out):
             self.s_out.wait_event(b["computed"])
-            host_out.copy_(b["out"], non_blocking=True)
+            host_out.copy_(o, non_blocking=True)
             b["stored"].record()
         self.n += 1
 
