@@ -218,13 +218,17 @@ class ExpertParallelMoE:
             idx, w = be.route(routing_logits, routing_bias, routed_scaling_factor)
             mark("route")
             px.push(hidden_states, hidden_states_scale, idx, w)
+            mark("push")
             px.barrier()
+            mark("barrier1")
             x_recv, sc_recv, idx_recv, w_recv = px.unpack()
-            mark("dispatch")
+            mark("unpack")
             part = be.experts(idx_recv, w_recv, x_recv, sc_recv)
             mark("experts")
             px.give_back(part, idx_recv)
+            mark("return")
             px.barrier()
+            mark("barrier2")
             out = px.combine(idx, T)
             mark("combine")
             return out
@@ -357,13 +361,17 @@ def bench(args, spec, name, rank, world, local):
         raise SystemExit(f"device error word {ep.peer.error_word()} in the peer-memory exchange")
     ep.last_plan = plan_dispatch(ep.backend.route(logits, bias, spec["rsf"])[0], shape.num_local_experts, world)
     nv = ep.nvlink_bytes()
-    phases = None
+    phases = phases_max = phases_min = None
     if torch.cuda.is_available():
         ep.phase_events = []
         for _ in range(min(K, 10)):
             step()
         phases = ep.phase_ms()
         ep.phase_events = None
+        allp = [None] * world
+        dist.all_gather_object(allp, phases)
+        phases_max = {k: max(p_[k] for p_ in allp) for k in phases}
+        phases_min = {k: min(p_[k] for p_ in allp) for k in phases}
 
     host_in = [t.cpu().pin_memory() for t in (logits, hidden, hscale)]
     dev_in = [torch.empty_like(t) for t in (logits, hidden, hscale)]
@@ -425,7 +433,7 @@ def bench(args, spec, name, rank, world, local):
                          "t_nvlink_ms": float(link) / 770e9 * 1e3},
             "layer": {"flops": flops, "tflops": flops / (ms_step * 1e-3) / 1e12, "pairs": float(pairs),
                       "rows_dispatched": float(n_recv), "max_link_bytes_per_rank": float(link)},
-            "phase_ms_rank0": phases,
+            "phase_ms_rank0": phases, "phase_ms_max_over_ranks": phases_max, "phase_ms_min_over_ranks": phases_min,
         }
         print(json.dumps(line))
     dist.barrier()
