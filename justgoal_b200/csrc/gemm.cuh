@@ -98,9 +98,10 @@ struct GemmCfg {
     // half-buffers in flight) - the N = 128 MMAs compete with the TMA fills for shared-memory bandwidth
     // and a K block took 750 ns instead of 570 ns.
     static constexpr int NTB = NACC;                        // TMEM hand-off barriers per direction
-    // promotion warps.  Measured: the fold of a 128 x 256 fp32 block takes ~1.1 us however the
-    // tcgen05.ld are chunked, batched or spread over 8 or 16 warps - it is bound by the TMEM read
-    // rate (~128 KB per K block), not by instruction issue or load latency.
+    // promotion warps: 4 (one per TMEM lane quarter) for narrow tiles, 8 (two column groups) from 64 tokens.
+    // With tokens on M the fold of a 128 x 256 fp32 block takes ~630 cycles: two tcgen05.ld round trips of
+    // 2 x 32 columns per thread (128 accumulator registers leave 64 for staging); 16 warps do not fit the
+    // register pool with a deeper staging and measured no gain with the same depth.
     static constexpr int NPW = NTOK >= 64 ? 8 : 4;
     static constexpr int NGRP = NPW / 4;                   // column groups (a group = 4 warps = all 128 lanes)
     static constexpr int NPT = 32 * NPW;                   // promotion threads
