@@ -95,16 +95,23 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_small_kernel(const Fro
         }
     }
 
-    // ---- gather: one warp per row, rows dealt round-robin over all warps of the grid
+    // ---- gather: a row is cut into GATHER_SPLIT pieces, one warp per piece, dealt round-robin over all warps of
+    // the grid: with a few dozen rows every lane then has 3-4 independent 16-byte loads in flight instead of 14
+    constexpr int GATHER_SPLIT = 4;
     const int H = fp.H, KB = H >> 7, rows_cap = pp.rows_cap;
-    for (int r = blockIdx.x * (FRONT_THREADS / 32) + warp; r < total_rows; r += gridDim.x * (FRONT_THREADS / 32)) {
+    const int chunks = H / 16, per_piece = (chunks + GATHER_SPLIT - 1) / GATHER_SPLIT;
+    const int n_tasks = total_rows * GATHER_SPLIT;
+    for (int task = blockIdx.x * (FRONT_THREADS / 32) + warp; task < n_tasks; task += gridDim.x * (FRONT_THREADS / 32)) {
+        const int r = task / GATHER_SPLIT, piece = task - r * GATHER_SPLIT;
         const int t = s_row_token[r];
         if (t < 0) continue;     // padding rows stay unwritten: their columns are never stored by the GEMMs
         uint4* dst = reinterpret_cast<uint4*>(fp.a_perm + (size_t)r * H);
         const uint4* src = reinterpret_cast<const uint4*>(fp.hidden + (size_t)t * H);
-        for (int i = lane; i < H / 16; i += 32) dst[i] = __ldg(src + i);
-        for (int kb = lane; kb < KB; kb += 32)
-            fp.a_scale_perm[(size_t)kb * rows_cap + r] = __ldg(fp.hscale + (size_t)kb * T + t);
+        const int c_end = min(chunks, (piece + 1) * per_piece);
+        for (int i = piece * per_piece + lane; i < c_end; i += 32) dst[i] = __ldg(src + i);
+        if (piece == 0)
+            for (int kb = lane; kb < KB; kb += 32)
+                fp.a_scale_perm[(size_t)kb * rows_cap + r] = __ldg(fp.hscale + (size_t)kb * T + t);
     }
 }
 
