@@ -179,6 +179,15 @@ int b200moe_ep_unpack_slots(b200moe_handle h, const void* wire, int n_slots, voi
                             void* cuda_stream);
 int b200moe_ep_return(b200moe_handle h, const void* partial_rows_bf16, const int32_t* topk_idx_slots,
                       int cap, int world, int my_rank, void* const* peer_back, void* cuda_stream);
+/* b200moe_forward_routed over the world*cap slots with b200moe_ep_return folded into its last kernel:
+ * the combine stores every present slot's bf16 row straight into the owner's back slot. */
+int b200moe_forward_routed_slots(b200moe_handle h, const int32_t* topk_idx, const float* topk_w,
+                                 const void* hidden_states, const void* hidden_states_scale,
+                                 const void* gemm1_weights, const void* gemm1_weights_scale,
+                                 const void* gemm2_weights, const void* gemm2_weights_scale,
+                                 int cap, int world, int my_rank, int local_expert_offset,
+                                 void* const* peer_back, void* workspace, size_t workspace_bytes,
+                                 void* cuda_stream);
 int b200moe_ep_combine_slots(b200moe_handle h, const void* back, const int32_t* topk_idx,
                              int num_tokens, int cap, int world, void* output_bf16, void* cuda_stream);
 

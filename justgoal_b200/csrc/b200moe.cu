@@ -244,7 +244,7 @@ inline cudaError_t prof_mark(b200moe_ctx* h, int point, cudaStream_t st) {
 int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
                 const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2, int T,
                 int local_offset, void* out, bool out_bf16, uint8_t* ws, const b200moe_ws_layout& L, cudaStream_t st,
-                bool fused_front = false) {
+                bool fused_front = false, const SlotOut* slot_out = nullptr) {
     const b200moe_config& c = h->cfg;
     const int El = c.num_local_experts, H = c.hidden, I = c.intermediate;
     const int ntok = (int)L.token_tile, rows_cap = (int)L.rows_cap;
@@ -334,12 +334,15 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     CU_TRY(prof_mark(h, 5, st));
 
     const int cgrid = T < h->num_sms * 8 ? T : h->num_sms * 8;
+    SlotOut so;
+    memset(&so, 0, sizeof(so));            // cap == 0: rows go to `out`
+    if (slot_out) so = *slot_out;
     if (out_bf16)
         CU_TRY(launch_k(PDL_COMBINE, combine_kernel<true>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
-                        (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El));
+                        (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
     else
         CU_TRY(launch_k(PDL_COMBINE, combine_kernel<false>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
-                        (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El));
+                        (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
     CU_TRY(prof_mark(h, 6, st));
     if (h->prof_slots) ++h->prof_calls;
     return 0;
@@ -622,6 +625,38 @@ int b200moe_ep_return(b200moe_handle h, const void* partial_rows, const int32_t*
         my_rank, pp);
     CU_TRY(cudaGetLastError());
     return 0;
+}
+
+int b200moe_forward_routed_slots(b200moe_handle h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
+                                 const void* hidden_scale, const void* w13, const void* s13, const void* w2,
+                                 const void* s2, int cap, int world, int my_rank, int local_offset,
+                                 void* const* peer_back, void* workspace, size_t workspace_bytes, void* stream) {
+    SlotOut so;
+    if (!h || cap < 1 || my_rank < 0 || my_rank >= world || !fill_peers(so.back, peer_back, world) ||
+        (long long)cap * world > 0x7FFFFFFF)
+        return B200MOE_E_BADARG;
+    if (!topk_idx || !topk_w || !hidden || !hidden_scale || !w13 || !s13 || !w2 || !s2) return B200MOE_E_BADARG;
+    so.cap = cap; so.my_rank = my_rank;
+    const int T = cap * world;
+    b200moe_ws_layout L;
+    int rc = check_ws(h, T, workspace, workspace_bytes, &L);
+    if (rc) return rc;
+    const b200moe_config& c = h->cfg;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    set_call_pdl(T);
+    CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
+    CU_TRY(prof_mark(h, 0, st));
+    const int n = T * c.top_k;
+    int grid = (n + 255) / 256;
+    if (grid > h->num_sms * 4) grid = h->num_sms * 4;
+    count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, local_offset, c.num_local_experts,
+                                       reinterpret_cast<int*>(ws + L.slices));
+    CU_TRY(cudaGetLastError());
+    CU_TRY(prof_mark(h, 1, st));
+    // the rows leave through the peer slots; `out` is never dereferenced in that mode
+    return run_experts(h, topk_idx, topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, ws, true, ws, L, st,
+                       false, &so);
 }
 
 int b200moe_ep_combine_slots(b200moe_handle h, const void* back, const int32_t* topk_idx, int T, int cap, int world,

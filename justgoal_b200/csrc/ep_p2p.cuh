@@ -16,10 +16,8 @@
 
 namespace b200moe {
 
-constexpr int EP_P2P_MAX_WORLD = 16;
 constexpr int ERR_WAIT_PEER = 7;           // a rank gave up waiting for a peer's barrier flag
-
-struct PeerPtrs { void* p[EP_P2P_MAX_WORLD]; };
+// (EP_P2P_MAX_WORLD and PeerPtrs live in permute.cuh: the combine kernel stores into peer slots too)
 
 // push: one warp per token slot t < cap of this rank.  Tokens t >= T (a step with fewer tokens than the
 // slots hold) are marked absent everywhere.

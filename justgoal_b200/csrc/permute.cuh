@@ -193,15 +193,29 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__
 // out[t, :] = sum over the token's local pairs (ascending expert order = the order they were
 // placed in topk rows is NOT sorted, so sort the <= 8 rows by row index, which is expert
 // order) of y[row, :]; fp32 accumulation, one rounding.  Tokens without a local pair get zeros.
+// Expert-parallel form (slots.cap > 0): "token" t is the slot (source rank t / cap, token t % cap) of the
+// peer-memory exchange; its row goes straight into that rank's buffer at slot (my_rank, token) - a plain
+// store over NVLink - and slots nobody filled (first expert id < 0) are skipped.
+constexpr int EP_P2P_MAX_WORLD = 16;
+struct PeerPtrs { void* p[EP_P2P_MAX_WORLD]; };
+struct SlotOut { PeerPtrs back; int cap; int my_rank; };
+
 template <bool OUT_BF16>
 __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ topk_idx,
                                                       const int32_t* __restrict__ pair_row, void* __restrict__ out,
-                                                      int T, int H, int top_k, int local_offset, int num_local) {
+                                                      int T, int H, int top_k, int local_offset, int num_local,
+                                                      const SlotOut slots) {
     __shared__ int s_rows[8];
     __shared__ int s_n;
     pdl_wait();
     pdl_launch();
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
+        __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)t * H;
+        if (OUT_BF16 && slots.cap > 0) {
+            if (topk_idx[(size_t)t * top_k] < 0) continue;          // same for the whole CTA
+            const int r = t / slots.cap;
+            out_row = static_cast<__nv_bfloat16*>(slots.back.p[r]) + ((size_t)slots.my_rank * slots.cap + (t - r * slots.cap)) * H;
+        }
         __syncthreads();
         if (threadIdx.x < 32) {
             // lanes 0..top_k-1 fetch their pair in parallel; rows are ranked by row index (= expert order)
@@ -236,7 +250,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
                 __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
                 for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + (size_t)t * H + h) = pk;
+                *reinterpret_cast<uint4*>(out_row + h) = pk;
             } else {
                 float* o = reinterpret_cast<float*>(out) + (size_t)t * H + h;
                 *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);

@@ -163,6 +163,18 @@ class PeerExchange:
                     "b200moe_ep_unpack_slots")
         return x, sc, idx, w
 
+    def experts_to_peers(self, idx, w, hidden, hscale, weights, offset):
+        """The local experts over all wire slots; the last kernel stores every present slot's bf16 row straight
+        into its owner's back slot (b200moe_forward_routed_slots: no intermediate buffer, no return copy)."""
+        n = self.world * self.cap
+        ws = self.layer.workspace(n)
+        self._keep2 = (idx, w, hidden, hscale)
+        ptrs = [t.data_ptr() for t in (idx, w, hidden, hscale, weights["gemm1_weights"], weights["gemm1_weights_scale"],
+                                       weights["gemm2_weights"], weights["gemm2_weights_scale"])]
+        self._check(self._lib.lib.b200moe_forward_routed_slots(self.layer._h, *ptrs, self.cap, self.world, self.rank,
+                                                               int(offset), self.peer_back, ws.data_ptr(), ws.numel(),
+                                                               self._stream()), "b200moe_forward_routed_slots")
+
     def give_back(self, part, idx_slots):
         self._check(self._lib.lib.b200moe_ep_return(self.layer._h, part.data_ptr(), idx_slots.data_ptr(), self.cap,
                                                     self.world, self.rank, self.peer_back, self._stream()),
@@ -223,10 +235,8 @@ class ExpertParallelMoE:
             mark("barrier1")
             x_recv, sc_recv, idx_recv, w_recv = px.unpack()
             mark("unpack")
-            part = be.experts(idx_recv, w_recv, x_recv, sc_recv)
+            px.experts_to_peers(idx_recv, w_recv, x_recv, sc_recv, be.w, be.offset)     # result rows go straight home
             mark("experts")
-            px.give_back(part, idx_recv)
-            mark("return")
             px.barrier()
             mark("barrier2")
             out = px.combine(idx, T)
@@ -425,7 +435,7 @@ def bench(args, spec, name, rank, world, local):
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             # per rank and step: route, pack | push + barrier, unpack, count, permute, gather, GEMM1, GEMM2, combine,
             # [return + barrier,] owner-side combine
-            "gpu_launches": (13 if exchange == "p2p" else 10) * K * world,
+            "gpu_launches": (12 if exchange == "p2p" else 10) * K * world,
             "roofline": {"kernel": "whole step, slowest rank", "bound": "hbm", "peak_source": "measured",
                          "achieved": w_bytes_rank / (ms_step * 1e-3) / 1e9, "peak": _hbm_peak(), "unit": "GB/s",
                          "frac": w_bytes_rank / (ms_step * 1e-3) / 1e9 / _hbm_peak(), "traffic": None,
