@@ -108,7 +108,7 @@ def workload_spec(name, n_gpus):
 
 
 # bias added to local experts 0, 8, 16, 24 so that they receive ~4x the mean load of the 32
-# local experts at T=4096 (calibrated once on the CPU with the seeded logits)
+# local experts at T=4096 (calibrated once on the CPU, by bisection, with the seeded logits)
 PREFILL_BIAS_BOOST = 0.328
 
 
