@@ -271,9 +271,8 @@ def cpu_baseline(shape, d, T, spec, budget_s=20.0, steps=1, warmup=0):
     The value is extrapolated to the whole step by the share of (token, expert) pairs covered."""
     from oracle import moe_oracle as O
     dc = _to_cpu(d)
-    idx, w = O.route_ds(dc["routing_logits"], dc["routing_bias"], shape.top_k, shape.n_group, shape.topk_group,
-                        spec["rsf"]) if shape.routing_mode == I.ROUTING_DS else O.route_renorm_naive(
-        dc["routing_logits"], dc["routing_bias"], shape.top_k, spec["rsf"])
+    idx, w = O.route(shape.routing_mode, dc["routing_logits"], dc["routing_bias"], shape.top_k, shape.n_group,
+                     shape.topk_group, spec["rsf"])
     off, El = dc["local_expert_offset"], shape.num_local_experts
     counts = [(int((idx == off + e).sum())) for e in range(El)]
     act = [e for e in range(El) if counts[e]]

@@ -26,6 +26,14 @@ extern "C" {
 
 #define B200MOE_ROUTING_DEEPSEEK 0      /* sigmoid + bias, group-limited top-k            */
 #define B200MOE_ROUTING_RENORM_NAIVE 1  /* softmax -> top-k -> renormalise (no groups)     */
+#define B200MOE_ROUTING_DEFAULT 2       /* softmax -> top-k, weights = probabilities        */
+#define B200MOE_ROUTING_RENORMALIZE 3   /* top-k on the logits -> softmax over the selected */
+#define B200MOE_ROUTING_LLAMA4 4        /* top-1 on the logits -> sigmoid (top_k must be 1) */
+#define B200MOE_ROUTING_TOPK 5          /* top-k on the logits, uniform weights factor/top_k */
+/* Modes 1-5: routing_bias, when given, is added to the logits first; every weight is multiplied by
+ * routed_scaling_factor.  The reference corpus ships only mode 0 (GF/moe_common.cuh:271-365); modes
+ * 1-5 follow the routing methods published with the operator family
+ * (flashinfer-python 0.6.11, flashinfer/trace/templates/moe.py:186-390). */
 
 #define B200MOE_E_BADARG   (-1)   /* null pointer, negative size, unsupported shape        */
 #define B200MOE_E_WORKSPACE (-2)  /* workspace too small or misaligned                     */
@@ -166,7 +174,8 @@ int b200moe_ep_unpack(b200moe_handle h, const void* wire, int n_rows, void* hidd
  *   b200moe_ep_combine_slots out[t] = fp32 sum, in rank order, of my back slots (r, t) over the ranks r
  *                            that own one of token t's experts; one rounding to bf16
  * peer_* are host arrays of `world` device addresses (entry r = the buffer part on rank r).
- * The barrier's wait gives up after 2 s and then stores 7 into *status_word (a device int the
+ * The barrier's wait gives up after the handle's wait limit (b200moe_set_wait_limit_ns, 2 s by
+ * default) and then stores 7 into *status_word (a device int the
  * caller owns and zeroes); the step's output is invalid in that case.  Only plain stores cross
  * NVLink.  (No counterpart in the reference.) */
 int b200moe_ep_push(b200moe_handle h, const void* hidden_states, const void* hidden_states_scale,
@@ -227,11 +236,27 @@ int b200moe_permute_noalloc(b200moe_handle h, const int32_t* topk_idx, const flo
                             int32_t* expert_row0, int32_t* row_token, float* row_w,
                             int rows_capacity, void* cuda_stream);
 
+/* Activation quantiser (the step before the operator): bf16 x[T, H] -> e4m3 q[T, H] and float
+ * scale[H/128, T] with scale = amax/448 over each (token, 128 columns) group (1.0 for an all-zero
+ * group) and q = round-to-nearest-even(x / scale): the operator's hidden_states /
+ * hidden_states_scale inputs.  x 16-byte aligned, H a multiple of 128.  The reference receives
+ * pre-quantised tensors from its harness (GF/moe_host.cu:100-103 checks their shapes) and has no
+ * such kernel; the grouping and the amax/448 rule are those of its input contract. */
+int b200moe_quantize_1x128(const void* x_bf16, int num_tokens, int hidden, void* q_e4m3,
+                           float* scale_kblock_major, void* cuda_stream);
+
 /* Synchronises the stream, reads the device error word of the last forward on this
  * workspace into *word (0 = no error) and returns B200MOE_E_KERNEL if it is non-zero.
  * The reference returns cudaGetLastError() only (KF94/kernel.cu:5681); its device waits
  * are unbounded, ours give up after a time limit and report here. */
 int b200moe_status(b200moe_handle h, const void* workspace, void* cuda_stream, int* word);
+
+/* How long a kernel of this handle waits for another RANK (the barrier flags of the peer-memory
+ * exchange) before it gives up, stores its error code and returns: 2 s by default, 1 ns .. 60 s.
+ * A rank that stopped between steps then costs its peers one limit, not a hang.  The waits inside
+ * one kernel (shared-memory stages, TMEM buffers) keep their fixed 2 s limit.  (No counterpart in
+ * the reference, whose device waits are unbounded.) */
+int b200moe_set_wait_limit_ns(b200moe_handle h, unsigned long long nanoseconds);
 
 /* Number of this library's kernels one forward over T tokens launches (a count of
  * launches, not of kernels that do useful work). */

@@ -9,7 +9,8 @@ it with `python -m justgoal_b200.build`): there is no CPU or PyTorch fallback.
 from .inputs import (DEEPSEEK_V3, QWEN3_MOE, TINY_DS, TINY_RENORM, MoEShape, ROUTING_DS,  # noqa: F401
                      ROUTING_RENORM_NAIVE)
 
-_LAZY = {"MoELayer": "main", "HostPipeline": "main", "run": "main", "run_dps": "main", "B200MoEError": "_lib"}
+_LAZY = {"MoELayer": "main", "HostPipeline": "main", "run": "main", "run_dps": "main", "quantize_1x128": "main",
+         "B200MoEError": "_lib"}
 
 
 def __getattr__(name):

@@ -50,6 +50,8 @@ def _load():
     lib.b200moe_forward_routed_slots.argtypes = [vp, vp, vp] + [vp] * 6 + [i, i, i, i, pv, vp, sz, vp]
     lib.b200moe_ep_pack.argtypes = [vp, vp, vp, vp, vp, vp, i, i, vp, vp]
     lib.b200moe_ep_unpack.argtypes = [vp, vp, i, vp, vp, vp, vp, vp]
+    lib.b200moe_set_wait_limit_ns.argtypes = [vp, C.c_ulonglong]
+    lib.b200moe_quantize_1x128.argtypes = [vp, i, i, vp, vp, vp]
     lib.b200moe_status.argtypes = [vp, vp, vp, C.POINTER(i)]
     lib.b200moe_launches_per_forward.argtypes = [vp, i, C.POINTER(i)]
     lib.b200moe_permute_noalloc.argtypes = [vp, vp, vp, i, i, vp, vp, vp, i, vp]
@@ -61,7 +63,7 @@ def _load():
     for name in ("create", "destroy", "workspace_bytes", "workspace_layout", "forward", "route",
                  "forward_routed", "status", "launches_per_forward", "num_sms", "profile_enable",
                  "profile_read", "permute_noalloc", "ep_combine", "ep_row_bytes", "ep_pack", "ep_unpack", "ep_push", "ep_barrier", "ep_unpack_slots",
-                 "ep_return", "ep_combine_slots", "forward_routed_slots"):
+                 "ep_return", "ep_combine_slots", "forward_routed_slots", "quantize_1x128", "set_wait_limit_ns"):
         getattr(lib, "b200moe_" + name).restype = i
     return lib
 

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
 SOURCES = ["b200moe.cu"]
-HEADERS = ["common.cuh", "routing.cuh", "permute.cuh", "front.cuh", "ep_p2p.cuh", "gemm.cuh", os.path.join("..", "..", "include", "b200moe.h")]
+HEADERS = ["common.cuh", "routing.cuh", "permute.cuh", "front.cuh", "ep_p2p.cuh", "gemm.cuh", "quant.cuh", os.path.join("..", "..", "include", "b200moe.h")]
 
 
 def _nvcc() -> str:

@@ -20,6 +20,7 @@
 #include "ep_p2p.cuh"
 #include "gemm.cuh"
 #include "permute.cuh"
+#include "quant.cuh"
 #include "routing.cuh"
 
 using namespace b200moe;
@@ -34,6 +35,7 @@ struct b200moe_ctx {
     long long prof_calls;      // forwards recorded since profiling was enabled
     cudaEvent_t* prof_events;  // [prof_slots][PROF_POINTS]
     int ablate;                // B200MOE_ABLATE environment variable at create (timing experiments; 0 in normal use)
+    unsigned long long wait_limit_ns;   // limit of the waits on a PEER (barrier flags); b200moe_set_wait_limit_ns
 };
 
 namespace {
@@ -207,7 +209,9 @@ bool cfg_ok(const b200moe_config& c) {
         if (gs < 2) return false;                         // group score needs two experts
         if (c.topk_group <= 0 || c.topk_group > c.n_group) return false;
         if (c.topk_group * gs < c.top_k) return false;    // enough candidates for top_k
-    } else if (c.routing_mode != B200MOE_ROUTING_RENORM_NAIVE) {
+    } else if (c.routing_mode == B200MOE_ROUTING_LLAMA4) {
+        if (c.top_k != 1) return false;                   // by definition a single expert per token
+    } else if (c.routing_mode < 0 || c.routing_mode >= RM_COUNT) {
         return false;
     }
     return true;
@@ -228,7 +232,14 @@ cudaError_t launch_route(int vpt, const RouteParams& rp, cudaStream_t st) {
 
 cudaError_t do_route(const b200moe_config& c, const RouteParams& rp, cudaStream_t st) {
     const int vpt = c.num_experts / 32;
-    return c.routing_mode == B200MOE_ROUTING_DEEPSEEK ? launch_route<0>(vpt, rp, st) : launch_route<1>(vpt, rp, st);
+    switch (c.routing_mode) {
+        case B200MOE_ROUTING_DEEPSEEK: return launch_route<RM_DEEPSEEK>(vpt, rp, st);
+        case B200MOE_ROUTING_RENORM_NAIVE: return launch_route<RM_RENORM_NAIVE>(vpt, rp, st);
+        case B200MOE_ROUTING_DEFAULT: return launch_route<RM_DEFAULT>(vpt, rp, st);
+        case B200MOE_ROUTING_RENORMALIZE: return launch_route<RM_RENORMALIZE>(vpt, rp, st);
+        case B200MOE_ROUTING_LLAMA4: return launch_route<RM_LLAMA4>(vpt, rp, st);
+        default: return launch_route<RM_TOPK>(vpt, rp, st);
+    }
 }
 
 #define CU_TRY(expr) do { cudaError_t e_ = (expr); if (e_ != cudaSuccess) return (int)e_; } while (0)
@@ -394,6 +405,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     if (!h) return B200MOE_E_BADARG;
     h->cfg = *cfg; h->device = dev; h->num_sms = sms;
     h->prof_slots = 0; h->prof_calls = 0; h->prof_events = nullptr;
+    h->wait_limit_ns = WAIT_LIMIT_NS;
 #ifdef B200MOE_ENABLE_ABLATE
     const char* ab = getenv("B200MOE_ABLATE");
     h->ablate = ab ? atoi(ab) : 0;
@@ -408,6 +420,12 @@ int b200moe_destroy(b200moe_handle h) {
     if (!h) return B200MOE_E_BADARG;
     b200moe_profile_enable(h, 0);
     delete h;
+    return 0;
+}
+
+int b200moe_set_wait_limit_ns(b200moe_handle h, unsigned long long ns) {
+    if (!h || ns == 0 || ns > 60ull * 1000000000ull) return B200MOE_E_BADARG;
+    h->wait_limit_ns = ns;
     return 0;
 }
 
@@ -597,7 +615,8 @@ int b200moe_ep_barrier(b200moe_handle h, void* const* peer_flags, int world, int
     PeerPtrs pp;
     if (!h || my_rank < 0 || my_rank >= world || !status_word || !fill_peers(pp, peer_flags, world))
         return B200MOE_E_BADARG;
-    ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, my_rank, epoch, status_word);
+    ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, world, my_rank, epoch, status_word,
+                                                                       h->wait_limit_ns);
     CU_TRY(cudaGetLastError());
     return 0;
 }
@@ -735,6 +754,21 @@ int b200moe_permute_noalloc(b200moe_handle h, const int32_t* topk_idx, const flo
     pp.pair_row = reinterpret_cast<int32_t*>(scratch + NOALLOC_HEAD_BYTES + NOALLOC_SLICE_BYTES);
     pp.expert_row0 = expert_row0; pp.row_token = row_token; pp.row_w = row_w; pp.rows_cap = rows_capacity;
     permute_kernel<<<ns, PERMUTE_THREADS, 0, st>>>(pp);
+    CU_TRY(cudaGetLastError());
+    return 0;
+}
+
+int b200moe_quantize_1x128(const void* x_bf16, int T, int H, void* q_e4m3, float* scale, void* stream) {
+    if (T < 0 || H <= 0 || H % 128) return B200MOE_E_BADARG;
+    if (T == 0) return 0;
+    if (!x_bf16 || !q_e4m3 || !scale) return B200MOE_E_BADARG;
+    if ((reinterpret_cast<uintptr_t>(x_bf16) & 15) || (reinterpret_cast<uintptr_t>(q_e4m3) & 7)) return B200MOE_E_BADARG;
+    const int sms = b200moe_num_sms();
+    const long long groups = (long long)T * (H >> 7);
+    long long grid = (groups + 15) / 16;                   // 16 groups (half warps) per CTA
+    if (grid > (long long)sms * 16) grid = (long long)sms * 16;
+    quantize_1x128_kernel<<<(int)(grid < 1 ? 1 : grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(x_bf16), T, H, static_cast<uint8_t*>(q_e4m3), scale);
     CU_TRY(cudaGetLastError());
     return 0;
 }

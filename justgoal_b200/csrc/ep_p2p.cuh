@@ -9,7 +9,8 @@
 // return (bf16 result rows stored straight into the owner's back slot) -> barrier -> owner sums.
 // Only plain peer stores cross NVLink (no multimem, no TMA on peer memory).  The barrier is a flag
 // exchange with release/acquire at system scope; its wait is bounded like every wait in this library
-// (gives up after WAIT_LIMIT_NS, records ERR_WAIT_PEER, the step's result is then invalid).
+// (gives up after the handle's wait limit - 2 s unless b200moe_set_wait_limit_ns changed it - records
+// ERR_WAIT_PEER and returns; the step's result is then invalid).
 // The reference has no distributed code; nothing here has a counterpart in it.
 #pragma once
 #include "permute.cuh"
@@ -54,7 +55,8 @@ __global__ void __launch_bounds__(256) ep_push_kernel(const uint8_t* __restrict_
 
 // barrier: rank `my_rank` writes `epoch` into flags[my_rank] of every rank, then waits until its own
 // flags[r] has reached `epoch` for every r.  One warp.  Epochs only grow, so flags are never reset.
-__global__ void __launch_bounds__(32) ep_barrier_kernel(PeerPtrs flags, int world, int my_rank, uint32_t epoch, int* status) {
+__global__ void __launch_bounds__(32) ep_barrier_kernel(PeerPtrs flags, int world, int my_rank, uint32_t epoch, int* status,
+                                                        unsigned long long limit_ns) {
     const int r = threadIdx.x;
     __threadfence_system();            // everything this rank stored before the barrier, to every peer
     if (r < world) {
@@ -66,8 +68,8 @@ __global__ void __launch_bounds__(32) ep_barrier_kernel(PeerPtrs flags, int worl
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
             if ((int32_t)(v - epoch) >= 0) break;
-            if ((it & 0xFFu) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
-                atomicCAS(status, 0, ERR_WAIT_PEER);
+            if ((it & 0x3Fu) == 0 && globaltimer_ns() - t0 > limit_ns) {
+                atomicCAS(status, 0, ERR_WAIT_PEER);       // give up: the kernel returns, the host reads the word
                 break;
             }
         }

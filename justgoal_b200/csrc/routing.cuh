@@ -7,6 +7,11 @@
 // computed from the UNBIASED sigmoid.  The reference kernels state the same rules
 // (goal_full_shape/fable-5.1/moe_fp8_fwd/<def>/moe_common.cuh:271-365,
 //  kda05_reproduction_full_shape/fable-5.1/moe_fp8_fwd/<def>/fable51_moe_v94/kernel.cu:125-204).
+// The other modes are the remaining routing methods of the same operator family (published with
+// the definition as softmax -> top-k "default", top-k -> softmax "renormalize", Llama-4 top-1 ->
+// sigmoid, and plain top-k with uniform weights); the reference corpus only ships the DeepSeek
+// variant, so those follow the published definitions alone.  In all of them the bias, when
+// given, is added to the logits before anything else.
 // All comparisons and arithmetic are IEEE fp32 (this file must not be built with fast-math);
 // exp is evaluated in fp64 and rounded once so that the fp32 result is the correctly rounded
 // one wherever the host's exp is.
@@ -15,6 +20,10 @@
 #include "common.cuh"
 
 namespace b200moe {
+
+// routing modes (B200MOE_ROUTING_* in the C header)
+enum : int { RM_DEEPSEEK = 0, RM_RENORM_NAIVE = 1, RM_DEFAULT = 2, RM_RENORMALIZE = 3, RM_LLAMA4 = 4, RM_TOPK = 5,
+             RM_COUNT = 6 };
 
 struct RouteParams {
     const float* logits;          // [T, E]
@@ -46,7 +55,7 @@ __device__ __forceinline__ void route_token(const RouteParams& p, int t, int lan
     for (int i = 0; i < VPT; ++i) s[i] = __ldg(row + i);
 
     bool kept = true;
-    if (MODE == 0) {
+    if (MODE == RM_DEEPSEEK) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const float e = (float)exp(-(double)s[i]);
@@ -76,7 +85,8 @@ __device__ __forceinline__ void route_token(const RouteParams& p, int t, int lan
             better += (og > gscore) || (og == gscore && g < my_group);
         }
         kept = better < p.topk_group;
-    } else {
+    } else if (MODE == RM_RENORM_NAIVE || MODE == RM_DEFAULT) {
+        // softmax over all experts; the selection ranks by the probabilities
         float mx = -INFINITY;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
@@ -90,6 +100,13 @@ __device__ __forceinline__ void route_token(const RouteParams& p, int t, int lan
         for (int off = 16; off; off >>= 1) sum += __shfl_xor_sync(FULL, sum, off);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) { s[i] = __fdiv_rn(s[i], sum); v[i] = s[i]; }
+    } else {
+        // top-k on the raw (biased) logits; the weights come from the selected logits afterwards
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            if (p.bias) s[i] = __fadd_rn(s[i], __bfloat162float(p.bias[lane * VPT + i]));
+            v[i] = s[i];
+        }
     }
 
     uint32_t key[VPT];
@@ -120,7 +137,23 @@ __device__ __forceinline__ void route_token(const RouteParams& p, int t, int lan
         if (lane == r) { sel_id = win * VPT + wi; sel_s = ws; }
         ssum = __fadd_rn(ssum, ws);
     }
-    w = __fmul_rn(__fdiv_rn(sel_s, __fadd_rn(ssum, 1e-20f)), p.scale);
+    if (MODE == RM_DEEPSEEK || MODE == RM_RENORM_NAIVE) {
+        w = __fmul_rn(__fdiv_rn(sel_s, __fadd_rn(ssum, 1e-20f)), p.scale);
+    } else if (MODE == RM_DEFAULT) {
+        w = __fmul_rn(sel_s, p.scale);
+    } else if (MODE == RM_RENORMALIZE) {
+        // softmax over the top_k selected logits; selection 0 is the largest of them
+        const float m0 = __shfl_sync(FULL, sel_s, 0);
+        const float e = lane < p.top_k ? (float)exp((double)__fsub_rn(sel_s, m0)) : 0.f;
+        float esum = e;
+        for (int off = 16; off; off >>= 1) esum += __shfl_xor_sync(FULL, esum, off);
+        w = __fmul_rn(__fdiv_rn(e, esum), p.scale);
+    } else if (MODE == RM_LLAMA4) {
+        const float e = (float)exp(-(double)sel_s);
+        w = __fmul_rn(__fdiv_rn(1.0f, __fadd_rn(1.0f, e)), p.scale);
+    } else {
+        w = (float)((double)p.scale / (double)p.top_k);
+    }
 }
 
 template <int VPT, int MODE>

@@ -36,17 +36,34 @@ class DispatchPlan:
     row_of: torch.Tensor            # int32 [world, T]
 
 
-def plan_dispatch(topk_idx: torch.Tensor, experts_per_rank: int, world: int, group=None) -> DispatchPlan:
-    """De-duplicated per (token, destination rank): a token with several experts on one rank is
-    sent there once.  One host synchronisation (the split sizes NCCL needs on the host)."""
+def _dispatch_mask(topk_idx: torch.Tensor, experts_per_rank: int, world: int):
     T, dev = topk_idx.shape[0], topk_idx.device
     dst = torch.div(topk_idx.long(), experts_per_rank, rounding_mode="floor").clamp_(0, world - 1)   # [T, K]
     mask = torch.zeros(world, T, dtype=torch.int32, device=dev)
     mask.scatter_(0, dst.t().contiguous(), 1)                     # mask[r, t] = 1 iff token t has an expert on rank r
     within = torch.cumsum(mask, dim=1, dtype=torch.int32)         # inclusive rank of token t among rank r's rows
     send_counts = within[:, -1].contiguous() if T else torch.zeros(world, dtype=torch.int32, device=dev)
-    recv_counts = torch.empty_like(send_counts)
-    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    return mask, within, send_counts
+
+
+def send_counts_of(topk_idx: torch.Tensor, experts_per_rank: int, world: int) -> torch.Tensor:
+    """int32 [world]: rows this rank's tokens send to every rank (what plan_dispatch exchanges)."""
+    return _dispatch_mask(topk_idx, experts_per_rank, world)[2]
+
+
+def plan_dispatch(topk_idx: torch.Tensor, experts_per_rank: int, world: int, group=None,
+                  recv_counts: torch.Tensor = None) -> DispatchPlan:
+    """De-duplicated per (token, destination rank): a token with several experts on one rank is
+    sent there once.  One host synchronisation (the split sizes NCCL needs on the host).
+    `recv_counts` (int32 [world], rows every rank sends to this one) replaces the counts all-to-all when
+    the caller already knows it - a single process that plays several ranks does."""
+    T, dev = topk_idx.shape[0], topk_idx.device
+    mask, within, send_counts = _dispatch_mask(topk_idx, experts_per_rank, world)
+    if recv_counts is None:
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=group)
+    else:
+        recv_counts = recv_counts.to(device=dev, dtype=send_counts.dtype)
     both = torch.stack([send_counts, recv_counts]).cpu()          # the one host sync of a step
     send, recv = both[0].tolist(), both[1].tolist()
     n_send = sum(send)
@@ -101,24 +118,43 @@ class PeerExchange:
 
     FLAGS_BYTES = 4096          # flags uint32[16] at 0, device status int at 1024
 
-    def __init__(self, layer, shape: MoEShape, cap: int, group, device):
+    @staticmethod
+    def buffer_bytes(layer, shape: MoEShape, cap: int, world: int) -> int:
+        wire_bytes = world * int(cap) * layer.ep_row_bytes()
+        back_off = (PeerExchange.FLAGS_BYTES + wire_bytes + 255) // 256 * 256
+        return back_off + world * int(cap) * shape.hidden * 2
+
+    def __init__(self, layer, shape: MoEShape, cap: int, group, device, local_buffers=None, rank=None):
+        """`local_buffers` (a list of `world` zeroed uint8 tensors of `buffer_bytes` bytes on THIS device, entry r
+        standing in for rank r's buffer) with `rank` builds the exchange without symmetric memory or a process
+        group: one process then plays every rank in turn on one GPU (tests)."""
         import ctypes as C
-        import torch.distributed._symmetric_memory as symm
         from . import _lib
         self._lib, self._C = _lib, C
         self.layer, self.shape, self.cap = layer, shape, int(cap)
         device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if local_buffers is None:
+            self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        else:
+            self.rank, self.world = int(rank), len(local_buffers)
         self.row_bytes = layer.ep_row_bytes()
         wire_bytes = self.world * self.cap * self.row_bytes
         back_bytes = self.world * self.cap * shape.hidden * 2
         self.wire_off = self.FLAGS_BYTES
         self.back_off = (self.wire_off + wire_bytes + 255) // 256 * 256
         total = self.back_off + back_bytes
-        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
-        self.buf.zero_()
-        self.handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
-        bases = [int(p) for p in self.handle.buffer_ptrs]
+        assert total == self.buffer_bytes(layer, shape, cap, self.world)
+        if local_buffers is None:
+            import torch.distributed._symmetric_memory as symm
+            self.buf = symm.empty(total, dtype=torch.uint8, device=device)
+            self.buf.zero_()
+            self.handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+            bases = [int(p) for p in self.handle.buffer_ptrs]
+        else:
+            if any(b.numel() < total or b.dtype != torch.uint8 or not b.is_cuda for b in local_buffers):
+                raise ValueError("local_buffers must be CUDA uint8 tensors of at least buffer_bytes() bytes")
+            self.buf, self.handle = local_buffers[self.rank], None
+            bases = [int(b.data_ptr()) for b in local_buffers]
         arr = C.c_void_p * self.world
         self.peer_flags = arr(*bases)
         self.peer_wire = arr(*[b + self.wire_off for b in bases])
@@ -127,9 +163,11 @@ class PeerExchange:
         self.wire = self.buf[self.wire_off:self.wire_off + wire_bytes].view(self.world * self.cap, self.row_bytes)
         self.back = self.buf[self.back_off:self.back_off + back_bytes].view(torch.bfloat16).view(
             self.world * self.cap, shape.hidden)
+        self.flags = self.buf[:64].view(torch.int32)          # uint32[16] arrival flags, entry r written by rank r
         self.epoch = 0
         torch.cuda.synchronize(device)
-        dist.barrier(group)           # every rank's flags are zero before anyone's first barrier kernel
+        if local_buffers is None:
+            dist.barrier(group)       # every rank's flags are zero before anyone's first barrier kernel
 
     def _stream(self):
         return self._C.c_void_p(torch.cuda.current_stream(self.buf.device).cuda_stream)
@@ -190,6 +228,9 @@ class PeerExchange:
     def error_word(self) -> int:
         """Device status of the barriers (0 = fine, 7 = a wait for a peer ran out).  Synchronises."""
         return int(self.status.item())
+
+    def clear_error(self):
+        self.status.zero_()
 
 
 class ExpertParallelMoE:
@@ -266,6 +307,17 @@ class ExpertParallelMoE:
         mark("combine")
         return out
 
+    def check_status(self):
+        """Raises if a barrier of the peer-memory exchange gave up waiting for a peer since the last check (the
+        outputs of that step are then invalid).  Synchronises the device, so call it where a synchronisation
+        is acceptable - e.g. once per batch of steps - not inside a latency-critical loop."""
+        if self.peer is not None:
+            word = self.peer.error_word()
+            if word != 0:
+                self.peer.clear_error()
+                raise RuntimeError(f"expert-parallel exchange: device error word {word} "
+                                   "(7 = a rank gave up waiting for a peer's barrier flag)")
+
     # ---- optional phase timing (CUDA events on the current stream; off unless `phase_events` is a list)
     phase_events = None
 
@@ -298,163 +350,3 @@ class ExpertParallelMoE:
         row = (s.hidden + 4 * (s.hidden // 128) + 8 * s.top_k + 15) // 16 * 16
         return {"dispatch_send": remote_send * row, "combine_send": remote_recv * 2 * s.hidden,
                 "dispatch_recv": remote_recv * row, "combine_recv": remote_send * 2 * s.hidden}
-
-
-# ---------------------------------------------------------------------------------------------
-# benchmark leg for bench.py (N > 1)
-# ---------------------------------------------------------------------------------------------
-def bench(args, spec, name, rank, world, local):
-    """One step = one expert-parallel forward of the whole layer over T tokens (T/world per rank).
-    Timed with CUDA events between barriers; the step time is the maximum over ranks."""
-    import json
-    import time
-
-    from . import inputs as I
-
-    dev = torch.device("cuda", local)
-    shape, T = spec["shape"], spec["T"]
-    per = T // world
-    tokens = I.make_tokens(shape, T, seed=0, device=dev)
-    sl = slice(rank * per, (rank + 1) * per)
-    logits = tokens["routing_logits"][sl].contiguous()
-    bias = tokens["routing_bias"]
-    hidden = tokens["hidden_states"].view(torch.uint8)[sl].contiguous().view(torch.float8_e4m3fn)
-    hscale = tokens["hidden_states_scale"][:, sl].contiguous()
-    weights = I.make_weights(shape, 0, dev, rank * shape.num_local_experts)
-    # Exchange: this library's kernels over peer memory when the node can map it and one step of it agrees
-    # with the NCCL form on the real inputs; else the NCCL form (B200MOE_EP_EXCHANGE=nccl|p2p forces one).
-    import os
-    want = os.environ.get("B200MOE_EP_EXCHANGE", "auto")
-    ep_nccl = ExpertParallelMoE(shape, weights, device=dev)
-    ep, exchange, why = ep_nccl, "nccl", "forced" if want == "nccl" else ""
-    if want != "nccl":
-        ok = torch.ones(1, device=dev)
-        try:
-            ep_p2p = ExpertParallelMoE(shape, weights, device=dev, exchange="p2p", capacity=per)
-            a = ep_nccl.forward(logits, bias, hidden, hscale, spec["rsf"])
-            b = ep_p2p.forward(logits, bias, hidden, hscale, spec["rsf"])
-            torch.cuda.synchronize()
-            if ep_p2p.peer.error_word() != 0 or not torch.allclose(a.float(), b.float(), atol=1e-2, rtol=1e-2):
-                ok.zero_(); why = "peer-memory step differs from the NCCL step"
-        except Exception as e:           # noqa: BLE001 - any failure to set the mapping up means: use NCCL
-            ok.zero_(); why = f"peer-memory setup failed: {type(e).__name__}"
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if float(ok) > 0:
-            ep, exchange = ep_p2p, "p2p"
-        elif want == "p2p":
-            raise SystemExit(f"B200MOE_EP_EXCHANGE=p2p but {why or 'another rank failed'}")
-    K, W = args.steps, max(args.warmup, 3)
-
-    def sync_time(fn, steps):
-        for _ in range(W):
-            fn()
-        torch.cuda.synchronize(); dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize(); dist.barrier()
-        t = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t)
-
-    out = None
-
-    def step():
-        nonlocal out
-        out = ep.forward(logits, bias, hidden, hscale, spec["rsf"])
-
-    sync_time(step, 2)           # untimed: first use of the barrier / all-reduce / event path itself
-    ms_step = sync_time(step, K)
-    if ep.peer is not None and ep.peer.error_word() != 0:
-        raise SystemExit(f"device error word {ep.peer.error_word()} in the peer-memory exchange")
-    ep.last_plan = plan_dispatch(ep.backend.route(logits, bias, spec["rsf"])[0], shape.num_local_experts, world)
-    nv = ep.nvlink_bytes()
-    phases = phases_max = phases_min = None
-    if torch.cuda.is_available():
-        ep.phase_events = []
-        for _ in range(min(K, 10)):
-            step()
-        phases = ep.phase_ms()
-        ep.phase_events = None
-        allp = [None] * world
-        dist.all_gather_object(allp, phases)
-        phases_max = {k: max(p_[k] for p_ in allp) for k in phases}
-        phases_min = {k: min(p_[k] for p_ in allp) for k in phases}
-
-    host_in = [t.cpu().pin_memory() for t in (logits, hidden, hscale)]
-    dev_in = [torch.empty_like(t) for t in (logits, hidden, hscale)]
-    host_out = torch.empty(per, shape.hidden, dtype=torch.bfloat16).pin_memory()
-
-    # host-resident inputs: the package's HostPipeline (copy in, step, copy out on three streams) around the
-    # expert-parallel step; every step moves its own inputs and output
-    from .main import HostPipeline
-    pipe = HostPipeline(ep.backend.layer, per, bias, None, None, None, None, 0, spec["rsf"],
-                        forward_fn=lambda lg, hd, sc, o: ep.forward(lg, bias, hd, sc, spec["rsf"]))
-    del dev_in
-
-    def e2e_round(steps):
-        for _ in range(steps):
-            pipe.step(host_in[0], host_in[1], host_in[2], host_out)
-        pipe.drain()
-
-    e2e_round(W)
-    torch.cuda.synchronize(); dist.barrier()
-    t0 = time.perf_counter()
-    e2e_round(K)
-    te = torch.tensor([(time.perf_counter() - t0) * 1e3 / K], device=dev)
-    dist.barrier()
-    dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_ms = float(te)
-    h2d = sum(t.numel() * t.element_size() for t in host_in) * world
-    d2h = host_out.numel() * host_out.element_size() * world
-
-    # realised work over all ranks
-    n_recv = torch.tensor([sum(ep.last_plan.recv_counts)], device=dev, dtype=torch.float64)
-    idx, _ = ep.backend.route(logits, bias, spec["rsf"])
-    pairs = torch.tensor([float(idx.numel())], device=dev, dtype=torch.float64)
-    link = torch.tensor([float(max(nv["dispatch_send"] + nv["combine_send"], nv["dispatch_recv"] + nv["combine_recv"]))],
-                        device=dev, dtype=torch.float64)
-    dist.all_reduce(pairs); dist.all_reduce(n_recv); dist.all_reduce(link, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        H, Iz = shape.hidden, shape.intermediate
-        flops = 6 * float(pairs) * H * Iz
-        w_bytes_rank = shape.num_local_experts * 3 * H * Iz
-        line = {
-            "metric": "moe_layer_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": K, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> f32 (block-scaled), bf16 out", "data": "synthetic",
-            "config": {"workload": f"{name}: T={T} per step over {world} ranks, hidden {H}, intermediate {Iz}, "
-                                   f"{shape.num_local_experts} of {shape.num_experts} experts per rank, top-{shape.top_k}, "
-                                   + ("expert parallel (dispatch/combine by this library's kernels over peer memory)"
-                                      if exchange == "p2p" else "expert parallel (NCCL all-to-all dispatch/combine)"),
-                       "exchange": exchange, "exchange_note": why,
-                       "l2": "inputs larger than L2 (%.2f GB of expert weights per rank)" % (w_bytes_rank / 1e9)},
-            "e2e": {"value": T / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-            # per rank and step: route, pack | push + barrier, unpack, count, permute, gather, GEMM1, GEMM2, combine,
-            # [return + barrier,] owner-side combine
-            "gpu_launches": (12 if exchange == "p2p" else 10) * K * world,
-            "roofline": {"kernel": "whole step, slowest rank", "bound": "hbm", "peak_source": "measured",
-                         "achieved": w_bytes_rank / (ms_step * 1e-3) / 1e9, "peak": _hbm_peak(), "unit": "GB/s",
-                         "frac": w_bytes_rank / (ms_step * 1e-3) / 1e9 / _hbm_peak(), "traffic": None,
-                         "t_hbm_ms": w_bytes_rank / _hbm_peak() / 1e6, "t_fp8_ms": flops / world / 4.5e15 * 1e3,
-                         "t_nvlink_ms": float(link) / 770e9 * 1e3},
-            "layer": {"flops": flops, "tflops": flops / (ms_step * 1e-3) / 1e12, "pairs": float(pairs),
-                      "rows_dispatched": float(n_recv), "max_link_bytes_per_rank": float(link)},
-            "phase_ms_rank0": phases, "phase_ms_max_over_ranks": phases_max, "phase_ms_min_over_ranks": phases_min,
-        }
-        print(json.dumps(line))
-    dist.barrier()
-    dist.destroy_process_group()
-
-
-def _hbm_peak():
-    import json
-    import os
-    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
-    try:
-        return float(json.load(open(p))["hbm_gbs"])
-    except Exception:
-        return 6650.0

@@ -18,7 +18,11 @@ BLOCK = 128
 FP8_MAX = 448.0
 
 ROUTING_DS = 0
-ROUTING_RENORM_NAIVE = 1
+ROUTING_RENORM_NAIVE = 1     # softmax -> top-k -> renormalise
+ROUTING_DEFAULT = 2          # softmax -> top-k
+ROUTING_RENORMALIZE = 3      # top-k -> softmax over the selected logits
+ROUTING_LLAMA4 = 4           # top-1 -> sigmoid
+ROUTING_TOPK = 5             # top-k, uniform weights
 
 
 @dataclass(frozen=True)
@@ -45,6 +49,10 @@ TINY_DS = MoEShape(hidden=512, intermediate=256, num_experts=64, num_local_exper
                    top_k=8, n_group=8, topk_group=4, routing_mode=ROUTING_DS)
 TINY_RENORM = MoEShape(hidden=384, intermediate=128, num_experts=32, num_local_experts=8,
                        top_k=4, n_group=1, topk_group=1, routing_mode=ROUTING_RENORM_NAIVE)
+TINY_DEFAULT = replace(TINY_RENORM, routing_mode=ROUTING_DEFAULT)
+TINY_RENORMALIZE = replace(TINY_RENORM, routing_mode=ROUTING_RENORMALIZE)
+TINY_LLAMA4 = replace(TINY_RENORM, top_k=1, routing_mode=ROUTING_LLAMA4)
+TINY_TOPK = replace(TINY_RENORM, routing_mode=ROUTING_TOPK)
 
 
 def _gen(seed, tensor_id, device):
@@ -80,10 +88,10 @@ def make_tokens(shape: MoEShape, T: int, seed: int = 0, device="cpu", bias_boost
     (the skewed-load prefill configuration)."""
     E, H = shape.num_experts, shape.hidden
     logits = torch.randn(T, E, generator=_gen(seed, 1, device), device=device, dtype=torch.float32)
-    if shape.routing_mode == ROUTING_DS:
-        bias = torch.randn(E, generator=_gen(seed, 2, device), device=device, dtype=torch.float32) * 0.1
+    if shape.routing_mode == ROUTING_RENORM_NAIVE:
+        bias = torch.zeros(E, device=device, dtype=torch.float32)    # the Qwen3-MoE configuration states no bias
     else:
-        bias = torch.zeros(E, device=device, dtype=torch.float32)
+        bias = torch.randn(E, generator=_gen(seed, 2, device), device=device, dtype=torch.float32) * 0.1
     if bias_boost is not None:
         ids, delta = bias_boost
         bias[torch.as_tensor(list(ids), device=device)] += float(delta)

@@ -101,6 +101,10 @@ class MoELayer:
         _lib.check(_lib.lib.b200moe_profile_read(self._h, int(slot), ms), "b200moe_profile_read")
         return dict(zip(self.STAGES, [float(x) for x in ms]))
 
+    def set_wait_limit(self, seconds: float):
+        """Limit of this layer's waits on another rank (barrier flags of the peer-memory exchange)."""
+        _lib.check(_lib.lib.b200moe_set_wait_limit_ns(self._h, int(seconds * 1e9)), "b200moe_set_wait_limit_ns")
+
     def status(self, T: int) -> int:
         word = C.c_int(0)
         stream = torch.cuda.current_stream(self.device).cuda_stream
@@ -248,6 +252,21 @@ class MoELayer:
                 raise ValueError(f"{name}: expected {dt} {shape}, got {t.dtype} {tuple(t.shape)}")
             if not t.is_cuda:
                 raise ValueError(f"{name} must be a CUDA tensor")
+
+
+def quantize_1x128(x: torch.Tensor):
+    """bf16 [T, H] on the GPU -> (e4m3 [T, H], float scales [H/128, T]): the operator's `hidden_states` and
+    `hidden_states_scale` inputs, made by the library's quantiser kernel on the current stream."""
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_cuda:
+        raise ValueError("x must be a CUDA bf16 [T, H] tensor")
+    x = _contig(x)
+    T, H = int(x.shape[0]), int(x.shape[1])
+    q = torch.empty(T, H, dtype=torch.float8_e4m3fn, device=x.device)
+    sc = torch.empty(H // 128, T, dtype=torch.float32, device=x.device)
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    _lib.check(_lib.lib.b200moe_quantize_1x128(_ptr(x), T, H, _ptr(q), _ptr(sc), C.c_void_p(stream)),
+               "b200moe_quantize_1x128")
+    return q, sc
 
 
 _layers = {}

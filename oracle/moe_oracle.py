@@ -8,10 +8,11 @@ ships no CPU/PyTorch implementation of the layer; the definition's arithmetic li
 third-party flashinfer-bench harness, un-vendored and un-pinned by the reference
 (README.md:51-56,60-66).  The same definition family is published in the wheel
 `flashinfer-python 0.6.11.post2` (flashinfer/trace/templates/moe.py,
-`_trtllm_fp8_block_scale_moe_ds_routing_reference` and
-`_trtllm_fp8_block_scale_moe_renormalize_naive_routing_reference`); this file restates that
-published algorithm and is pinned against outputs of those two functions through the
-fixtures in tests/golden/ (made by tests/golden/make_golden.py).
+`_trtllm_fp8_block_scale_moe_ds_routing_reference`,
+`_trtllm_fp8_block_scale_moe_renormalize_naive_routing_reference` and the four other routing
+methods of the family); this file restates that published algorithm and is pinned against
+outputs of those functions through the fixtures in tests/golden/ (made by
+tests/golden/make_golden.py).
 
 Only tests/, __graft_entry__.smoke() and the CPU-baseline legs of bench.py may import this
 module, and only as the checker.  The product path never calls it.
@@ -42,6 +43,10 @@ BLOCK = 128
 
 ROUTING_DS = 0            # DeepSeek-V3: sigmoid + bias, group-limited top-k
 ROUTING_RENORM_NAIVE = 1  # softmax -> top-k -> renormalise (Qwen3-MoE shape)
+ROUTING_DEFAULT = 2       # softmax -> top-k
+ROUTING_RENORMALIZE = 3   # top-k on the logits -> softmax over the selected
+ROUTING_LLAMA4 = 4        # top-1 -> sigmoid
+ROUTING_TOPK = 5          # top-k, uniform weights
 
 
 @dataclass
@@ -100,6 +105,62 @@ def route_renorm_naive(routing_logits, routing_bias, top_k, routed_scaling_facto
     g = s.gather(1, topk_idx)
     w = g / (g.sum(dim=1, keepdim=True) + 1e-20)
     return topk_idx, w * routed_scaling_factor
+
+
+def _biased_logits(routing_logits, routing_bias):
+    logits = routing_logits.to(torch.float32)
+    if routing_bias is not None:
+        logits = logits + routing_bias.to(torch.float32).reshape(-1)
+    return logits
+
+
+@torch.no_grad()
+def route_default(routing_logits, routing_bias, top_k, routed_scaling_factor):
+    """Softmax over all experts -> top-k; the weights are the selected probabilities
+    (published as `..._default_routing_reference`, flashinfer/trace/templates/moe.py:186-224)."""
+    s = torch.softmax(_biased_logits(routing_logits, routing_bias), dim=-1)
+    _, topk_idx = torch.topk(s, k=int(top_k), dim=1, largest=True, sorted=False)
+    return topk_idx, s.gather(1, topk_idx) * routed_scaling_factor
+
+
+@torch.no_grad()
+def route_renormalize(routing_logits, routing_bias, top_k, routed_scaling_factor):
+    """Top-k on the logits -> softmax over the selected logits (`..._renormalize_routing_reference`,
+    same file :226-265)."""
+    logits = _biased_logits(routing_logits, routing_bias)
+    _, topk_idx = torch.topk(logits, k=int(top_k), dim=1, largest=True, sorted=False)
+    return topk_idx, torch.softmax(logits.gather(1, topk_idx), dim=-1) * routed_scaling_factor
+
+
+@torch.no_grad()
+def route_llama4(routing_logits, routing_bias, top_k, routed_scaling_factor):
+    """Top-1 on the logits, weight = sigmoid of that logit (`..._llama4_routing_reference`, :267-306)."""
+    logits = _biased_logits(routing_logits, routing_bias)
+    topk_idx = logits.argmax(dim=-1, keepdim=True)
+    top1 = logits.gather(1, topk_idx)
+    return topk_idx, (1.0 / (1.0 + torch.exp(-top1))) * routed_scaling_factor
+
+
+@torch.no_grad()
+def route_topk(routing_logits, routing_bias, top_k, routed_scaling_factor):
+    """Top-k on the logits, every selected expert weighs factor / top_k (`..._topk_routing_reference`,
+    :350-390)."""
+    logits = _biased_logits(routing_logits, routing_bias)
+    _, topk_idx = torch.topk(logits, k=int(top_k), dim=1, largest=True, sorted=False)
+    w = torch.full(topk_idx.shape, routed_scaling_factor / int(top_k), dtype=torch.float32)
+    return topk_idx, w
+
+
+def route(routing_mode, routing_logits, routing_bias, top_k, n_group, topk_group, routed_scaling_factor):
+    """Dispatch on the routing mode; (topk_idx int64 [T, top_k], topk_w fp32 [T, top_k])."""
+    rsf = float(routed_scaling_factor)
+    if routing_mode == ROUTING_DS:
+        return route_ds(routing_logits, routing_bias, top_k, n_group, topk_group, rsf)
+    fn = {ROUTING_RENORM_NAIVE: route_renorm_naive, ROUTING_DEFAULT: route_default,
+          ROUTING_RENORMALIZE: route_renormalize, ROUTING_LLAMA4: route_llama4, ROUTING_TOPK: route_topk}.get(routing_mode)
+    if fn is None:
+        raise ValueError(f"unknown routing_mode {routing_mode}")
+    return fn(routing_logits, routing_bias, top_k, rsf)
 
 
 def _dequant_weight(w_fp8, scale):
@@ -164,13 +225,7 @@ def moe_forward(routing_logits, routing_bias, hidden_states, hidden_states_scale
                 top_k=8, n_group=8, topk_group=4, keep_inter=False) -> OracleResult:
     """The whole layer for one rank's experts; all tensors on the CPU."""
     E_global = routing_logits.shape[1]
-    if routing_mode == ROUTING_DS:
-        idx, w = route_ds(routing_logits, routing_bias, top_k, n_group, topk_group,
-                          float(routed_scaling_factor))
-    elif routing_mode == ROUTING_RENORM_NAIVE:
-        idx, w = route_renorm_naive(routing_logits, routing_bias, top_k, float(routed_scaling_factor))
-    else:
-        raise ValueError(f"unknown routing_mode {routing_mode}")
+    idx, w = route(routing_mode, routing_logits, routing_bias, top_k, n_group, topk_group, routed_scaling_factor)
     out, et, inter = run_experts(hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
                                  gemm2_weights, gemm2_weights_scale, w, idx, local_expert_offset,
                                  E_global, keep_inter=keep_inter)

@@ -32,6 +32,19 @@ CASES = {
     "tiny_ds_t7_off16": (I.TINY_DS, 7, 2, 16, 0.05),
     "tiny_renorm_t20": (I.TINY_RENORM, 20, 3, 8, 0.08),
     "ds_v3_t16": (I.DEEPSEEK_V3, 16, 0, 0, 0.02),   # configs[0] of the benchmark definition
+    # the other routing methods of the operator family
+    "tiny_default_t20": (I.TINY_DEFAULT, 20, 4, 8, 0.08),
+    "tiny_renormalize_t20": (I.TINY_RENORMALIZE, 20, 5, 8, 0.08),
+    "tiny_llama4_t40": (I.TINY_LLAMA4, 40, 6, 8, 0.08),
+    "tiny_topk_t20": (I.TINY_TOPK, 20, 7, 8, 0.08),
+}
+
+PUBLISHED = {     # routing mode -> name of the published reference function
+    I.ROUTING_RENORM_NAIVE: "_trtllm_fp8_block_scale_moe_renormalize_naive_routing_reference",
+    I.ROUTING_DEFAULT: "_trtllm_fp8_block_scale_moe_default_routing_reference",
+    I.ROUTING_RENORMALIZE: "_trtllm_fp8_block_scale_moe_renormalize_routing_reference",
+    I.ROUTING_LLAMA4: "_trtllm_fp8_block_scale_moe_llama4_routing_reference",
+    I.ROUTING_TOPK: "_trtllm_fp8_block_scale_moe_topk_routing_reference",
 }
 
 
@@ -58,10 +71,10 @@ def main():
             idx, w = O.route_ds(d["routing_logits"], d["routing_bias"], shape.top_k, shape.n_group,
                                 shape.topk_group, d["routed_scaling_factor"])
         else:
-            ref = FM._trtllm_fp8_block_scale_moe_renormalize_naive_routing_reference(
+            ref = getattr(FM, PUBLISHED[shape.routing_mode])(
                 *args, shape.top_k, d["local_expert_offset"], d["routed_scaling_factor"])
-            idx, w = O.route_renorm_naive(d["routing_logits"], d["routing_bias"], shape.top_k,
-                                          d["routed_scaling_factor"])
+            idx, w = O.route(shape.routing_mode, d["routing_logits"], d["routing_bias"], shape.top_k, shape.n_group,
+                             shape.topk_group, d["routed_scaling_factor"])
         chk = FM._fp8_moe_run_experts(*args[2:], w, idx, d["local_expert_offset"], shape.num_experts)
         assert torch.equal(chk.view(torch.int16), ref.view(torch.int16)), name
         order = torch.argsort(idx, dim=1)

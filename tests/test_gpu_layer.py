@@ -34,7 +34,8 @@ def _assert_close(out, want_bf16, what):
     return rep
 
 
-@pytest.mark.parametrize("name", ["tiny_ds_t33", "tiny_ds_t7_off16", "tiny_renorm_t20", "ds_v3_t16"])
+@pytest.mark.parametrize("name", ["tiny_ds_t33", "tiny_ds_t7_off16", "tiny_renorm_t20", "ds_v3_t16",
+                                  "tiny_default_t20", "tiny_renormalize_t20", "tiny_llama4_t40", "tiny_topk_t20"])
 def test_layer_matches_golden_and_oracle(name):
     shape, d, g = util.golden_case(name)
     layer, out = _run(shape, d)

@@ -1,6 +1,8 @@
 """GPU: routing kernel through the C ABI (b200moe_route) against the oracle: selected expert
 SETS must be identical per token; weights within 4 ulp (the definition sums 256 mostly-zero
 terms in an unspecified order, so the last bits of the normaliser are not pinned)."""
+import dataclasses
+
 import pytest
 import torch
 
@@ -14,10 +16,8 @@ def _check(shape, T, seed, rsf, bias_none=False):
     from justgoal_b200 import MoELayer
     d = I.make_tokens(shape, T, seed)
     bias = None if bias_none else d["routing_bias"]
-    if shape.routing_mode == I.ROUTING_DS:
-        idx_o, w_o = O.route_ds(d["routing_logits"], bias, shape.top_k, shape.n_group, shape.topk_group, rsf)
-    else:
-        idx_o, w_o = O.route_renorm_naive(d["routing_logits"], bias, shape.top_k, rsf)
+    idx_o, w_o = O.route(shape.routing_mode, d["routing_logits"], bias, shape.top_k, shape.n_group,
+                         shape.topk_group, rsf)
     layer = MoELayer(shape)
     idx, w = layer.route(d["routing_logits"].cuda(), None if bias is None else bias.cuda(), rsf)
     torch.cuda.synchronize()
@@ -52,3 +52,12 @@ def test_tiny_group_structure():
 @pytest.mark.parametrize("shape", [I.QWEN3_MOE, I.TINY_RENORM])
 def test_softmax_topk_renormalise(shape):
     _check(shape, 2048, seed=3, rsf=1.0)
+
+
+@pytest.mark.parametrize("shape", [I.TINY_DEFAULT, I.TINY_RENORMALIZE, I.TINY_LLAMA4, I.TINY_TOPK,
+                                   dataclasses.replace(I.QWEN3_MOE, routing_mode=I.ROUTING_RENORMALIZE)])
+def test_other_routing_methods_of_the_family(shape):
+    """softmax -> top-k, top-k -> softmax, Llama-4 top-1 -> sigmoid, plain top-k: sets exact, weights within
+    the softmax tolerance, with a bias and without."""
+    _check(shape, 1500, seed=9, rsf=1.5)
+    _check(shape, 33, seed=10, rsf=1.0, bias_none=True)

@@ -7,7 +7,8 @@ import torch
 import util
 from util import O
 
-CASES = ["tiny_ds_t33", "tiny_ds_t7_off16", "tiny_renorm_t20", "ds_v3_t16"]
+CASES = ["tiny_ds_t33", "tiny_ds_t7_off16", "tiny_renorm_t20", "ds_v3_t16",
+         "tiny_default_t20", "tiny_renormalize_t20", "tiny_llama4_t40", "tiny_topk_t20"]
 
 
 @pytest.mark.parametrize("name", CASES)
