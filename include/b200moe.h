@@ -41,6 +41,7 @@ extern "C" {
 #define B200MOE_E_DEVICE   (-4)   /* not an sm_100 device                                  */
 #define B200MOE_E_KERNEL   (-5)   /* a kernel recorded a device-side error (see status)    */
 #define B200MOE_E_TOO_LARGE (-6)  /* more tokens than the allocation-free entry point holds */
+#define B200MOE_E_BUILD    (-7)   /* library built with an unexpected register allocation   */
 
 #define B200MOE_NOALLOC_MAX_TOKENS 8192
 
@@ -127,6 +128,11 @@ int b200moe_forward(b200moe_handle h,
 int b200moe_route(b200moe_handle h, const void* routing_logits, const void* routing_bias,
                   int num_tokens, float routed_scaling_factor,
                   int32_t* topk_idx, float* topk_w, void* cuda_stream);
+
+/* Entry points that take topk_idx from the caller (b200moe_forward_routed, _forward_routed_slots,
+ * _permute_noalloc) expect the ids of one token's row to be DISTINCT (ids < 0 or outside the local
+ * range are ignored): the row buffers hold min(top_k, E_local) rows per token.  A row that repeats a
+ * local expert is refused on the device: error word 5, rows beyond the capacity are not written. */
 
 /* The expert part alone, for tokens that were routed elsewhere (expert-parallel receive
  * side): like b200moe_forward but takes topk_idx/topk_w instead of logits, and writes the

@@ -35,7 +35,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
     cmd = [_nvcc(), "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
-           "-shared", "-Xcompiler", "-fPIC",
+           "-shared", "-Xcompiler", "-fPIC", "-I", os.path.join(HERE, "..", "include"),
            "-o", LIB] + [os.path.join(CSRC, s) for s in SOURCES]
     extra = os.environ.get("B200MOE_NVCC_FLAGS")      # e.g. -DB200MOE_ENABLE_ABLATE for timing experiments
     if extra:

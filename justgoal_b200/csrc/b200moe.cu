@@ -14,7 +14,7 @@
 #include <mutex>
 #include <new>
 
-#include "../../include/b200moe.h"
+#include "b200moe.h"
 #include "common.cuh"
 #include "front.cuh"
 #include "ep_p2p.cuh"
@@ -170,7 +170,7 @@ cudaError_t set_attr() {
         cudaFuncAttributes fa;
         cudaError_t e = cudaFuncGetAttributes(&fa, gemm_kernel<NTOK, G1>);
         if (e != cudaSuccess) return e;
-        if (fa.numRegs != C::LAUNCH_REGS) return cudaErrorInvalidConfiguration;
+        if (fa.numRegs != C::LAUNCH_REGS) return (cudaError_t)(-B200MOE_E_BUILD + 100000);   // decoded by CU_TRY_ATTR
     }
     return cudaFuncSetAttribute(gemm_kernel<NTOK, G1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
 }
@@ -397,10 +397,13 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     CU_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     if (major != 10) return B200MOE_E_DEVICE;
     if (!get_encode()) return B200MOE_E_DRIVER;
-    CU_TRY((set_attr<16, true>()));  CU_TRY((set_attr<16, false>()));
-    CU_TRY((set_attr<32, true>()));  CU_TRY((set_attr<32, false>()));
-    CU_TRY((set_attr<64, true>()));  CU_TRY((set_attr<64, false>()));
-    CU_TRY((set_attr<128, true>())); CU_TRY((set_attr<128, false>()));
+#define CU_TRY_ATTR(expr) do { cudaError_t e_ = (expr); if ((int)e_ == -B200MOE_E_BUILD + 100000) return B200MOE_E_BUILD; \
+                               if (e_ != cudaSuccess) return (int)e_; } while (0)
+    CU_TRY_ATTR((set_attr<16, true>()));  CU_TRY_ATTR((set_attr<16, false>()));
+    CU_TRY_ATTR((set_attr<32, true>()));  CU_TRY_ATTR((set_attr<32, false>()));
+    CU_TRY_ATTR((set_attr<64, true>()));  CU_TRY_ATTR((set_attr<64, false>()));
+    CU_TRY_ATTR((set_attr<128, true>())); CU_TRY_ATTR((set_attr<128, false>()));
+#undef CU_TRY_ATTR
     b200moe_ctx* h = new (std::nothrow) b200moe_ctx;
     if (!h) return B200MOE_E_BADARG;
     h->cfg = *cfg; h->device = dev; h->num_sms = sms;
@@ -486,6 +489,7 @@ int b200moe_route(b200moe_handle h, const void* logits, const void* bias, int T,
     rp.T = T; rp.E = c.num_experts; rp.top_k = c.top_k; rp.n_group = c.n_group; rp.topk_group = c.topk_group;
     rp.local_offset = 0; rp.num_local = 0; rp.scale = scale; rp.topk_idx = topk_idx; rp.topk_w = topk_w;
     rp.slices = nullptr;
+    g_call_pdl = 0;                       // a stand-alone launch: nothing before it to overlap with
     CU_TRY(do_route(c, rp, static_cast<cudaStream_t>(stream)));
     return 0;
 }
@@ -789,6 +793,8 @@ const char* b200moe_strerror(int code) {
         case B200MOE_E_DRIVER: return "cuTensorMapEncodeTiled unavailable or failed";
         case B200MOE_E_DEVICE: return "device is not compute capability 10.x";
         case B200MOE_E_KERNEL: return "a kernel gave up a bounded wait or met a bad schedule (see status word)";
+        case B200MOE_E_BUILD: return "a GEMM kernel was compiled with a register count other than the one its setmaxnreg "
+                                     "arithmetic assumes (different compiler version or flags): rebuild with the stated nvcc";
         case B200MOE_E_TOO_LARGE: return "num_tokens exceeds B200MOE_NOALLOC_MAX_TOKENS (the static scratch array is fixed-size)";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
     }

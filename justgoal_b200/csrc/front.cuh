@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_small_kernel(const Fro
     // ---- scan
     if (warp == 0) scan_counts(s_cnt, El, pp.token_tile, s_row0, s_tiles, publish ? pp.status : nullptr, lane);
     __syncthreads();
-    const int total_rows = s_row0[El];
+    const int total_rows = min(min(s_row0[El], FRONT_MAX_ROWS), pp.rows_cap);
     if (publish) {
         for (int i = tid; i <= El; i += blockDim.x) {
             pp.expert_row0[i] = s_row0[i];
@@ -80,8 +80,12 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_small_kernel(const Fro
             const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
             if (hit) {
                 const int r = s_row0[e] + placed + __popc(m & ((1u << lane) - 1u));
-                s_row_token[r] = i / K;
-                if (publish) { pp.pair_row[i] = r; pp.row_w[r] = s_w[i]; }
+                if (r < FRONT_MAX_ROWS && r < pp.rows_cap) {
+                    s_row_token[r] = i / K;
+                    if (publish) { pp.pair_row[i] = r; pp.row_w[r] = s_w[i]; }
+                } else {                    // repeated expert ids inside a caller-given row: refuse, write nothing
+                    atomicCAS(pp.status + ST_ERR, 0, ERR_BAD_SCHEDULE);
+                }
             }
             placed += __popc(m);
         }

@@ -156,13 +156,20 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const PlanPara
         }
         // padding rows of every segment carry token -1
         for (int e = warp; e < El; e += 32)
-            for (int r = s_row0[e] + s_cnt[e] + lane; r < s_row0[e + 1]; r += 32) { p.row_token[r] = -1; p.row_w[r] = 0.f; }
+            for (int r = s_row0[e] + s_cnt[e] + lane; r < min(s_row0[e + 1], p.rows_cap); r += 32) {
+                p.row_token[r] = -1; p.row_w[r] = 0.f;
+            }
     }
     if (local) {
         const int r = s_row0[le] + s_before[le] + s_wcnt[warp][le] + rank;
-        p.pair_row[i] = r;
-        p.row_token[r] = i / p.top_k;
-        p.row_w[r] = p.topk_w[i];
+        if (r < p.rows_cap) {
+            p.pair_row[i] = r;
+            p.row_token[r] = i / p.top_k;
+            p.row_w[r] = p.topk_w[i];
+        } else {
+            // only reachable with expert ids from the caller that repeat an expert inside one token's row
+            atomicCAS(p.status + ST_ERR, 0, ERR_BAD_SCHEDULE);
+        }
     }
 }
 

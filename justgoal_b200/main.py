@@ -227,10 +227,23 @@ class MoELayer:
         scratch in a static device array (for hosts that must not allocate device memory); at most
         `_lib.NOALLOC_MAX_TOKENS` tokens, calls on one device must not overlap."""
         T = int(topk_idx.shape[0])
-        stream = torch.cuda.current_stream(topk_idx.device).cuda_stream
+        dev = topk_idx.device
+        for name, t, dt in (("topk_idx", topk_idx, torch.int32), ("topk_w", topk_w, torch.float32),
+                            ("expert_row0", expert_row0, torch.int32), ("row_token", row_token, torch.int32),
+                            ("row_w", row_w, torch.float32)):
+            if t.dtype != dt or not t.is_cuda or t.device != dev:
+                raise ValueError(f"{name} must be a {dt} CUDA tensor on {dev}")
+        for name, t in (("expert_row0", expert_row0), ("row_token", row_token), ("row_w", row_w)):
+            if not t.is_contiguous():
+                raise ValueError(f"{name} must be contiguous (it is written in place)")
+        if tuple(topk_idx.shape) != (T, self.shape.top_k) or tuple(topk_w.shape) != (T, self.shape.top_k):
+            raise ValueError("topk_idx / topk_w must be [T, top_k]")
+        if expert_row0.numel() < self.shape.num_local_experts + 1:
+            raise ValueError("expert_row0 needs num_local_experts + 1 entries")
+        stream = torch.cuda.current_stream(dev).cuda_stream
         rc = _lib.lib.b200moe_permute_noalloc(self._h, _ptr(_contig(topk_idx)), _ptr(_contig(topk_w)), T,
                                               _scalar(local_expert_offset, int), _ptr(expert_row0),
-                                              _ptr(row_token), _ptr(row_w), int(row_token.numel()),
+                                              _ptr(row_token), _ptr(row_w), min(int(row_token.numel()), int(row_w.numel())),
                                               C.c_void_p(stream))
         _lib.check(rc, "b200moe_permute_noalloc")
 

@@ -1,0 +1,153 @@
+"""FP8 block-scale MoE layer (DeepSeek-V3 routing) for NVIDIA B200 - flashinfer-bench solution entry point.
+
+`run(...)` returns a fresh bf16 [T, 7168] tensor (non destination-passing); `run_dps(..., output)` writes into
+the caller's tensor.  Same argument list as the reference solutions' entry points
+(goal_full_shape/fable-5.1/moe_fp8_fwd/<def>/main.py:102-117 and, destination-passing,
+kda05_reproduction_full_shape/fable-5.1/moe_fp8_fwd/<def>/fable51_moe_v94/main.py:196-209).
+
+Self-contained: the CUDA sources that travel with this file (b200moe.cu and its headers, all in this
+directory) are compiled once with nvcc for sm_100a into a cache directory keyed by a hash of the sources,
+and loaded through ctypes (the C ABI of b200moe.h).  torch supplies tensors, the current stream and the
+workspace allocation only; there is no fallback if the build or the device is missing.
+"""
+import ctypes as C
+import hashlib
+import os
+import shutil
+import subprocess
+import tempfile
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SOURCES = ["b200moe.cu", "b200moe.h", "common.cuh", "routing.cuh", "permute.cuh", "front.cuh", "ep_p2p.cuh",
+            "gemm.cuh", "quant.cuh"]
+_LOCK = threading.Lock()
+_LIB = None
+_HANDLES = {}       # (H, I, E, E_local, device index) -> handle
+_WORKSPACES = {}    # (handle key, token bucket) -> uint8 tensor
+
+TOP_K, N_GROUP, TOPK_GROUP, ROUTING_DEEPSEEK = 8, 8, 4, 0
+
+
+class _Config(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("hidden", "intermediate", "num_experts", "num_local_experts", "top_k",
+                                       "n_group", "topk_group", "routing_mode")]
+
+
+def _nvcc():
+    cands = [os.environ.get("NVCC")]
+    for env in ("CUDA_HOME", "CUDA_PATH"):
+        if os.environ.get(env):
+            cands.append(os.path.join(os.environ[env], "bin", "nvcc"))
+    cands += [shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"]
+    for c in cands:
+        if c and os.path.isfile(c):
+            return c
+    raise RuntimeError("nvcc not found: the solution builds its CUDA library on first use")
+
+
+def _build():
+    """Path of the shared library, compiling it first if no build of these exact sources is cached."""
+    h = hashlib.sha256()
+    for f in _SOURCES:
+        with open(os.path.join(_HERE, f), "rb") as fh:
+            h.update(f.encode()); h.update(fh.read())
+    root = os.environ.get("B200MOE_BUILD_DIR") or os.path.join(os.path.expanduser("~"), ".cache", "b200moe_solution")
+    try:
+        os.makedirs(root, exist_ok=True)
+    except OSError:
+        root = os.path.join(tempfile.gettempdir(), "b200moe_solution")
+        os.makedirs(root, exist_ok=True)
+    so = os.path.join(root, "libb200moe_%s.so" % h.hexdigest()[:16])
+    if not os.path.isfile(so):
+        tmp = "%s.%d.tmp" % (so, os.getpid())
+        cmd = [_nvcc(), "-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a", "-shared",
+               "-Xcompiler", "-fPIC", "-I", _HERE, "-o", tmp, os.path.join(_HERE, "b200moe.cu")]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed:\n" + r.stdout + r.stderr)
+        os.replace(tmp, so)
+    return so
+
+
+def _lib():
+    global _LIB
+    with _LOCK:
+        if _LIB is None:
+            lib = C.CDLL(_build())
+            vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+            lib.b200moe_create.argtypes = [C.POINTER(_Config), C.POINTER(vp)]
+            lib.b200moe_workspace_bytes.argtypes = [vp, i, C.POINTER(sz)]
+            lib.b200moe_forward.argtypes = [vp] + [vp] * 8 + [i, i, f, vp, vp, sz, vp]
+            lib.b200moe_strerror.argtypes = [i]
+            lib.b200moe_strerror.restype = C.c_char_p
+            _LIB = lib
+    return _LIB
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise RuntimeError("%s failed with code %d: %s" % (what, rc, _lib().b200moe_strerror(rc).decode()))
+
+
+def _scalar(v, kind):
+    return kind(v.item() if isinstance(v, torch.Tensor) else v)
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _forward(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+             gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, output):
+    lib = _lib()
+    dev = hidden_states.device
+    T, H = int(hidden_states.shape[0]), int(hidden_states.shape[1])
+    if output is None:
+        output = torch.empty(T, H, dtype=torch.bfloat16, device=dev)      # a fresh tensor per call, never a cached one
+    if T == 0:
+        return output
+    key = (H, int(gemm1_weights.shape[1]) // 2, int(routing_logits.shape[1]), int(gemm1_weights.shape[0]), dev.index)
+    with torch.cuda.device(dev):
+        h = _HANDLES.get(key)
+        if h is None:
+            cfg = _Config(key[0], key[1], key[2], key[3], TOP_K, N_GROUP, TOPK_GROUP, ROUTING_DEEPSEEK)
+            h = C.c_void_p()
+            _check(lib.b200moe_create(C.byref(cfg), C.byref(h)), "b200moe_create")
+            _HANDLES[key] = h
+        bucket = 64
+        while bucket < T:
+            bucket *= 2
+        ws = _WORKSPACES.get((key, bucket))
+        if ws is None:
+            n = C.c_size_t()
+            _check(lib.b200moe_workspace_bytes(h, bucket, C.byref(n)), "b200moe_workspace_bytes")
+            ws = _WORKSPACES[(key, bucket)] = torch.empty(max(int(n.value), 256), dtype=torch.uint8, device=dev)
+        tensors = [None if t is None else t.contiguous() for t in (
+            routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+            gemm2_weights, gemm2_weights_scale)]
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        rc = lib.b200moe_forward(h, *[_ptr(t) for t in tensors], T, _scalar(local_expert_offset, int),
+                                 _scalar(routed_scaling_factor, float), _ptr(output), _ptr(ws), ws.numel(), stream)
+        _check(rc, "b200moe_forward")
+    return output
+
+
+@torch.no_grad()
+def run(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+        gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor):
+    return _forward(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                    gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                    routed_scaling_factor, None)
+
+
+@torch.no_grad()
+def run_dps(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+            gemm2_weights, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, output):
+    if output.dtype != torch.bfloat16 or not output.is_contiguous():
+        raise ValueError("output must be a contiguous bf16 [T, hidden] tensor")
+    return _forward(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                    gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                    routed_scaling_factor, output)

@@ -135,3 +135,31 @@ def test_reference_entry_point_signature():
     assert out.dtype == torch.bfloat16 and tuple(out.shape) == (16, 7168)
     golden = torch.from_numpy(g["output_bf16_bits"]).view(torch.bfloat16)
     _assert_close(out, golden, "run() vs golden")
+
+
+def test_packed_solution_runs_the_operator(tmp_path, monkeypatch):
+    """The flashinfer-bench package (solution/solution.json unpacked into a fresh directory, built by its own
+    main.py) gives the same bits as the in-tree library, through both entry points."""
+    import importlib.util
+    import json
+    import os
+    from justgoal_b200 import run
+    m = json.load(open(os.path.join(util.ROOT, "solution", "solution.json")))
+    for src in m["sources"]:
+        open(os.path.join(tmp_path, src["path"]), "w").write(src["content"])
+    monkeypatch.setenv("B200MOE_BUILD_DIR", str(tmp_path / "build"))
+    spec = importlib.util.spec_from_file_location("packed_solution_gpu", os.path.join(tmp_path, "main.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    shape, d, g = util.golden_case("ds_v3_t16")
+    args = util.op_args(util.to_cuda(d))
+    want = run(*args)
+    got = mod.run(*args)
+    out = torch.full_like(want, 7.0)
+    ret = mod.run_dps(*args, out)
+    torch.cuda.synchronize()
+    assert ret.data_ptr() == out.data_ptr() and got.data_ptr() != want.data_ptr()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    golden = torch.from_numpy(g["output_bf16_bits"]).view(torch.bfloat16)
+    _assert_close(got, golden, "packed solution vs golden")
