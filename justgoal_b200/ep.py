@@ -307,6 +307,12 @@ class ExpertParallelMoE:
         mark("combine")
         return out
 
+    def launches_per_step(self) -> int:
+        """Kernels of this library one step launches on one rank.  Peer-memory form: route, push, barrier, slot
+        unpack, count, permute, gather, GEMM1, GEMM2, combine (stores into the owners' slots), barrier, owner-side
+        sum; collective form: route, pack, unpack, count, permute, gather, GEMM1, GEMM2, combine, owner-side sum."""
+        return 12 if self.peer is not None else 10
+
     def check_status(self):
         """Raises if a barrier of the peer-memory exchange gave up waiting for a peer since the last check (the
         outputs of that step are then invalid).  Synchronises the device, so call it where a synchronisation
