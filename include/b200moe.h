@@ -136,9 +136,11 @@ int b200moe_route(b200moe_handle h, const void* routing_logits, const void* rout
 
 /* The expert part alone, for tokens that were routed elsewhere (expert-parallel receive
  * side): like b200moe_forward but takes topk_idx/topk_w instead of logits, and writes the
- * sum over the LOCAL experts to output [T, H]: fp32 when output_is_bf16 == 0 (no rounding,
- * so partial sums of several ranks can be added before the single final rounding), bf16
- * rows (one rounding of the local sum, the form that travels back over NVLink) otherwise.
+ * sum over the LOCAL experts to output [T, H]: output_kind 0 = fp32 (no rounding), 1 = bf16
+ * (the operator's output type: right when the local experts are all of a token's experts),
+ * 2 = fp16, the form PARTIAL rows travel in between ranks (two bytes like bf16 but 11
+ * significant bits: the owner adds the partial rows of up to world ranks in fp32 before the
+ * single rounding to bf16, and bf16 partials cost that sum the output tolerance).
  * The reference has no expert-parallel code; this corresponds to the launcher's stages
  * after routing (KF94/kernel.cu:5436-5586). */
 int b200moe_forward_routed(b200moe_handle h,
@@ -147,7 +149,7 @@ int b200moe_forward_routed(b200moe_handle h,
                            const void* gemm1_weights, const void* gemm1_weights_scale,
                            const void* gemm2_weights, const void* gemm2_weights_scale,
                            int num_tokens, int local_expert_offset,
-                           void* output, int output_is_bf16, void* workspace, size_t workspace_bytes,
+                           void* output, int output_kind, void* workspace, size_t workspace_bytes,
                            void* cuda_stream);
 
 /* Expert-parallel dispatch rows.  One row on the wire carries all a receiving rank needs for one
@@ -168,13 +170,13 @@ int b200moe_ep_unpack(b200moe_handle h, const void* wire, int n_rows, void* hidd
 /* The same exchange over peer memory (NVLink) instead of a library all-to-all.  Every rank owns one
  * buffer that all ranks of the node have mapped (how it is shared - symmetric memory, CUDA IPC - is
  * the host's business; this library only receives the peer addresses):
- *   flags uint32[16], zero before the first step; wire [world][cap] dispatch rows; back [world][cap][H] bf16.
+ *   flags uint32[16], zero before the first step; wire [world][cap] dispatch rows; back [world][cap][H] fp16.
  * A step on every rank, all launches on one stream, `cap` the same on all ranks, T <= cap:
  *   b200moe_ep_push          own tokens' rows stored into wire slot (my_rank, t) of every rank that owns
  *                            one of the token's experts; the slot of every other rank gets expert ids -1
  *   b200moe_ep_barrier       epoch e (strictly increasing over the life of the buffers)
  *   b200moe_ep_unpack_slots  my wire, all world*cap slots -> inputs of b200moe_forward_routed
- *   b200moe_forward_routed   over world*cap tokens, bf16 rows out
+ *   b200moe_forward_routed   over world*cap tokens, fp16 partial rows out (output_kind 2)
  *   b200moe_ep_return        result rows of present slots stored into back slot (my_rank, t) of the owner
  *   b200moe_ep_barrier       epoch e + 1
  *   b200moe_ep_combine_slots out[t] = fp32 sum, in rank order, of my back slots (r, t) over the ranks r
@@ -192,10 +194,10 @@ int b200moe_ep_barrier(b200moe_handle h, void* const* peer_flags, int world, int
 int b200moe_ep_unpack_slots(b200moe_handle h, const void* wire, int n_slots, void* hidden_states,
                             void* hidden_states_scale, int32_t* topk_idx, float* topk_w,
                             void* cuda_stream);
-int b200moe_ep_return(b200moe_handle h, const void* partial_rows_bf16, const int32_t* topk_idx_slots,
+int b200moe_ep_return(b200moe_handle h, const void* partial_rows_fp16, const int32_t* topk_idx_slots,
                       int cap, int world, int my_rank, void* const* peer_back, void* cuda_stream);
 /* b200moe_forward_routed over the world*cap slots with b200moe_ep_return folded into its last kernel:
- * the combine stores every present slot's bf16 row straight into the owner's back slot. */
+ * the combine stores every present slot's fp16 partial row straight into the owner's back slot. */
 int b200moe_forward_routed_slots(b200moe_handle h, const int32_t* topk_idx, const float* topk_w,
                                  const void* hidden_states, const void* hidden_states_scale,
                                  const void* gemm1_weights, const void* gemm1_weights_scale,
@@ -209,7 +211,8 @@ int b200moe_ep_combine_slots(b200moe_handle h, const void* back, const int32_t* 
 /* Expert-parallel combine on the token's owner rank: out[t, :] = sum over the ranks r that
  * computed a share of token t (row_of[r, t] >= 0) of partial_rows[row_of[r, t], :], added in
  * fp32 in ascending rank order, rounded once to bf16.  partial_rows is the receive buffer
- * of the combine all-to-all, bf16 [n_rows, H]; row_of is int32 [world, T].  Tokens without
+ * of the combine all-to-all, fp16 [n_rows, H] (b200moe_forward_routed with output_kind 2);
+ * row_of is int32 [world, T].  Tokens without
  * any share get zeros.  (No counterpart in the reference, which has no distributed code.) */
 int b200moe_ep_combine(b200moe_handle h, const void* partial_rows, const int32_t* row_of,
                        int world, int num_tokens, void* output_bf16, void* cuda_stream);

@@ -254,7 +254,7 @@ inline cudaError_t prof_mark(b200moe_ctx* h, int point, cudaStream_t st) {
 // Everything after routing: permute -> gather -> GEMM1 -> GEMM2 -> combine.
 int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
                 const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2, int T,
-                int local_offset, void* out, bool out_bf16, uint8_t* ws, const b200moe_ws_layout& L, cudaStream_t st,
+                int local_offset, void* out, int out_kind, uint8_t* ws, const b200moe_ws_layout& L, cudaStream_t st,
                 bool fused_front = false, const SlotOut* slot_out = nullptr) {
     const b200moe_config& c = h->cfg;
     const int El = c.num_local_experts, H = c.hidden, I = c.intermediate;
@@ -348,11 +348,14 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     SlotOut so;
     memset(&so, 0, sizeof(so));            // cap == 0: rows go to `out`
     if (slot_out) so = *slot_out;
-    if (out_bf16)
-        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<true>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
+    if (out_kind == OUT_BF16)
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_BF16>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
+                        (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
+    else if (out_kind == OUT_F16)
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F16>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
                         (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
     else
-        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<false>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F32>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
                         (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
     CU_TRY(prof_mark(h, 6, st));
     if (h->prof_slots) ++h->prof_calls;
@@ -522,14 +525,14 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     CU_TRY(do_route(c, rp, st));
     CU_TRY(prof_mark(h, 1, st));
     return run_experts(h, rp.topk_idx, rp.topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output,
-                       true, ws, L, st, fused);
+                       OUT_BF16, ws, L, st, fused);
 }
 
 int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
                            const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2,
-                           int T, int local_offset, void* output, int output_is_bf16, void* workspace,
+                           int T, int local_offset, void* output, int output_kind, void* workspace,
                            size_t workspace_bytes, void* stream) {
-    if (!h || T < 0) return B200MOE_E_BADARG;
+    if (!h || T < 0 || output_kind < 0 || output_kind > 2) return B200MOE_E_BADARG;
     if (T == 0) return 0;
     if (!topk_idx || !topk_w || !hidden || !hidden_scale || !w13 || !s13 || !w2 || !s2 || !output)
         return B200MOE_E_BADARG;
@@ -550,7 +553,7 @@ int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const floa
     CU_TRY(cudaGetLastError());
     CU_TRY(prof_mark(h, 1, st));
     return run_experts(h, topk_idx, topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output,
-                       output_is_bf16 != 0, ws, L, st);
+                       output_kind, ws, L, st);
 }
 
 int b200moe_ep_row_bytes(b200moe_handle h, int* bytes) {
@@ -644,7 +647,7 @@ int b200moe_ep_return(b200moe_handle h, const void* partial_rows, const int32_t*
         !fill_peers(pp, peer_back, world) || h->cfg.hidden % 8)
         return B200MOE_E_BADARG;
     ep_return_kernel<<<row_grid(h, (long long)world * cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(partial_rows), topk_idx_slots, cap, h->cfg.hidden, h->cfg.top_k, world,
+        static_cast<const __half*>(partial_rows), topk_idx_slots, cap, h->cfg.hidden, h->cfg.top_k, world,
         my_rank, pp);
     CU_TRY(cudaGetLastError());
     return 0;
@@ -678,7 +681,7 @@ int b200moe_forward_routed_slots(b200moe_handle h, const int32_t* topk_idx, cons
     CU_TRY(cudaGetLastError());
     CU_TRY(prof_mark(h, 1, st));
     // the rows leave through the peer slots; `out` is never dereferenced in that mode
-    return run_experts(h, topk_idx, topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, ws, true, ws, L, st,
+    return run_experts(h, topk_idx, topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, ws, OUT_F16, ws, L, st,
                        false, &so);
 }
 
@@ -691,7 +694,7 @@ int b200moe_ep_combine_slots(b200moe_handle h, const void* back, const int32_t* 
     if (!back || !topk_idx || !output_bf16) return B200MOE_E_BADARG;
     const int grid = T < h->num_sms * 8 ? T : h->num_sms * 8;
     ep_combine_slots_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(back), topk_idx, T, cap, h->cfg.hidden, h->cfg.top_k,
+        static_cast<const __half*>(back), topk_idx, T, cap, h->cfg.hidden, h->cfg.top_k,
         h->cfg.num_local_experts, world, static_cast<__nv_bfloat16*>(output_bf16));
     CU_TRY(cudaGetLastError());
     return 0;
@@ -706,7 +709,7 @@ int b200moe_ep_combine(b200moe_handle h, const void* partial_rows, const int32_t
     if (H % 8) return B200MOE_E_BADARG;
     int grid = T < h->num_sms * 8 ? T : h->num_sms * 8;
     ep_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(partial_rows), row_of, world, T, H, static_cast<__nv_bfloat16*>(output_bf16));
+        static_cast<const __half*>(partial_rows), row_of, world, T, H, static_cast<__nv_bfloat16*>(output_bf16));
     CU_TRY(cudaGetLastError());
     return 0;
 }

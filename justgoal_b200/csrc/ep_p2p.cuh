@@ -3,10 +3,10 @@
 // Every rank owns one symmetric buffer (same layout on all ranks, mapped into every peer):
 //   flags  uint32[EP_P2P_MAX_WORLD]        arrival flags of the barrier, flags[r] is written by rank r
 //   wire   [world][cap] dispatch rows      slot (source rank, token of that rank): what others pushed to me
-//   back   [world][cap][H] bf16            slot (expert rank, my token): partial results pushed back to me
+//   back   [world][cap][H] fp16            slot (expert rank, my token): partial results pushed back to me
 // A step: push (each token's row is stored straight into the wire slot of every rank that owns one of
 // its experts; the other ranks' slots get the marker id -1) -> barrier -> unpack + local experts ->
-// return (bf16 result rows stored straight into the owner's back slot) -> barrier -> owner sums.
+// return (fp16 partial rows stored straight into the owner's back slot) -> barrier -> owner sums.
 // Only plain peer stores cross NVLink (no multimem, no TMA on peer memory).  The barrier is a flag
 // exchange with release/acquire at system scope; its wait is bounded like every wait in this library
 // (gives up after the handle's wait limit - 2 s unless b200moe_set_wait_limit_ns changed it - records
@@ -102,7 +102,7 @@ __global__ void __launch_bounds__(256) ep_unpack_slots_kernel(const uint8_t* wir
 }
 
 // return: result row of slot (source rank r, token t) -> rank r's back slot (my_rank, t).  One warp per slot.
-__global__ void __launch_bounds__(256) ep_return_kernel(const __nv_bfloat16* __restrict__ part, const int32_t* __restrict__ topk_idx,
+__global__ void __launch_bounds__(256) ep_return_kernel(const __half* __restrict__ part, const int32_t* __restrict__ topk_idx,
                                                         int cap, int H, int top_k, int world, int my_rank, PeerPtrs back) {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -111,14 +111,14 @@ __global__ void __launch_bounds__(256) ep_return_kernel(const __nv_bfloat16* __r
         if (topk_idx[(size_t)i * top_k] < 0) continue;
         const int r = i / cap, t = i - r * cap;
         const uint4* src = reinterpret_cast<const uint4*>(part + (size_t)i * H);
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(back.p[r]) + ((size_t)my_rank * cap + t) * H);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__half*>(back.p[r]) + ((size_t)my_rank * cap + t) * H);
         for (int c = lane; c < H / 8; c += 32) dst[c] = __ldg(src + c);
     }
 }
 
 // owner-side sum over the back slots: like ep_combine_kernel, the set of ranks that hold a share of token t
 // is recomputed from the token's own expert ids.
-__global__ void __launch_bounds__(256) ep_combine_slots_kernel(const __nv_bfloat16* back,
+__global__ void __launch_bounds__(256) ep_combine_slots_kernel(const __half* back,
                                                                const int32_t* __restrict__ topk_idx, int T, int cap, int H,
                                                                int top_k, int experts_per_rank, int world,
                                                                __nv_bfloat16* __restrict__ out) {
@@ -135,19 +135,9 @@ __global__ void __launch_bounds__(256) ep_combine_slots_kernel(const __nv_bfloat
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int r = 0; r < world; ++r) {
                 if (!s_has[r]) continue;
-                const uint4 v = *reinterpret_cast<const uint4*>(back + ((size_t)r * cap + t) * H + h);
-                const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float2 f = __bfloat1622float2(v2[q]);
-                    acc[2 * q] += f.x; acc[2 * q + 1] += f.y;
-                }
+                add8_f16(acc, *reinterpret_cast<const uint4*>(back + ((size_t)r * cap + t) * H + h));
             }
-            uint4 pk;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
-            *reinterpret_cast<uint4*>(out + (size_t)t * H + h) = pk;
+            *reinterpret_cast<uint4*>(out + (size_t)t * H + h) = pack8_bf16(acc);
         }
     }
 }

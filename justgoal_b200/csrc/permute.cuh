@@ -9,6 +9,7 @@
 // goal_full_shape/fable-5.1/moe_fp8_fwd/<def>/moe_route.cuh:44-72.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include "common.cuh"
 
 namespace b200moe {
@@ -200,14 +201,44 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__
 // out[t, :] = sum over the token's local pairs (ascending expert order = the order they were
 // placed in topk rows is NOT sorted, so sort the <= 8 rows by row index, which is expert
 // order) of y[row, :]; fp32 accumulation, one rounding.  Tokens without a local pair get zeros.
+// Output kinds: fp32 rows (no rounding), bf16 rows (the operator's output: one rounding of the whole sum), or
+// fp16 rows - the PARTIAL rows of expert parallelism, which the token's owner adds up in fp32 before the one
+// rounding to bf16.  fp16 carries 11 significant bits against bf16's 8 at the same two bytes: with bf16
+// partials of up to four ranks per token about 3 in 100 000 output elements of the DeepSeek-V3 shape left the
+// 1e-2 / 1e-2 tolerance; partial sums stay far below fp16's range (|row| of order 10).
 // Expert-parallel form (slots.cap > 0): "token" t is the slot (source rank t / cap, token t % cap) of the
-// peer-memory exchange; its row goes straight into that rank's buffer at slot (my_rank, token) - a plain
+// peer-memory exchange; its fp16 row goes straight into that rank's buffer at slot (my_rank, token) - a plain
 // store over NVLink - and slots nobody filled (first expert id < 0) are skipped.
 constexpr int EP_P2P_MAX_WORLD = 16;
 struct PeerPtrs { void* p[EP_P2P_MAX_WORLD]; };
 struct SlotOut { PeerPtrs back; int cap; int my_rank; };
 
-template <bool OUT_BF16>
+enum : int { OUT_F32 = 0, OUT_BF16 = 1, OUT_F16 = 2 };
+
+__device__ __forceinline__ uint4 pack8_bf16(const float* a) {
+    uint4 pk;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(a[2 * q], a[2 * q + 1]);
+    return pk;
+}
+__device__ __forceinline__ uint4 pack8_f16(const float* a) {
+    uint4 pk;
+    __half2* o2 = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) o2[q] = __floats2half2_rn(a[2 * q], a[2 * q + 1]);
+    return pk;
+}
+__device__ __forceinline__ void add8_f16(float* acc, const uint4& v) {
+    const __half2* v2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float2 f = __half22float2(v2[q]);
+        acc[2 * q] += f.x; acc[2 * q + 1] += f.y;
+    }
+}
+
+template <int OUT>
 __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ topk_idx,
                                                       const int32_t* __restrict__ pair_row, void* __restrict__ out,
                                                       int T, int H, int top_k, int local_offset, int num_local,
@@ -217,11 +248,11 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
     pdl_wait();
     pdl_launch();
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
-        __nv_bfloat16* out_row = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)t * H;
-        if (OUT_BF16 && slots.cap > 0) {
+        uint16_t* out_row = reinterpret_cast<uint16_t*>(out) + (size_t)t * H;      // 2-byte kinds
+        if (OUT == OUT_F16 && slots.cap > 0) {
             if (topk_idx[(size_t)t * top_k] < 0) continue;          // same for the whole CTA
             const int r = t / slots.cap;
-            out_row = static_cast<__nv_bfloat16*>(slots.back.p[r]) + ((size_t)slots.my_rank * slots.cap + (t - r * slots.cap)) * H;
+            out_row = static_cast<uint16_t*>(slots.back.p[r]) + ((size_t)slots.my_rank * slots.cap + (t - r * slots.cap)) * H;
         }
         __syncthreads();
         if (threadIdx.x < 32) {
@@ -252,12 +283,10 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
                 acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
                 acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
             }
-            if (OUT_BF16) {
-                uint4 pk;
-                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
-                *reinterpret_cast<uint4*>(out_row + h) = pk;
+            if (OUT == OUT_BF16) {
+                *reinterpret_cast<uint4*>(out_row + h) = pack8_bf16(acc);
+            } else if (OUT == OUT_F16) {
+                *reinterpret_cast<uint4*>(out_row + h) = pack8_f16(acc);
             } else {
                 float* o = reinterpret_cast<float*>(out) + (size_t)t * H + h;
                 *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -315,10 +344,10 @@ __global__ void __launch_bounds__(256) ep_unpack_kernel(const uint8_t* __restric
 }
 
 // Expert-parallel combine on the owner rank: out[t] = sum over ranks r with row_of[r][t] >= 0 of
-// back[row_of[r][t]] (bf16 rows received from the ranks that own the token's experts), fp32, ascending
-// rank order, one rounding.  One CTA per token, 16 bytes per thread and step.
+// back[row_of[r][t]] (fp16 partial rows received from the ranks that own the token's experts), fp32,
+// ascending rank order, one rounding to bf16.  One CTA per token, 16 bytes per thread and step.
 constexpr int EP_MAX_WORLD = 64;
-__global__ void __launch_bounds__(256) ep_combine_kernel(const __nv_bfloat16* __restrict__ back,
+__global__ void __launch_bounds__(256) ep_combine_kernel(const __half* __restrict__ back,
                                                          const int32_t* __restrict__ row_of, int world, int T, int H,
                                                          __nv_bfloat16* __restrict__ out) {
     __shared__ int s_row[EP_MAX_WORLD];
@@ -331,19 +360,9 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const __nv_bfloat16* __
             for (int r = 0; r < world; ++r) {
                 const int row = s_row[r];
                 if (row < 0) continue;
-                const uint4 v = __ldg(reinterpret_cast<const uint4*>(back + (size_t)row * H + h));
-                const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float2 f = __bfloat1622float2(v2[q]);
-                    acc[2 * q] += f.x; acc[2 * q + 1] += f.y;
-                }
+                add8_f16(acc, __ldg(reinterpret_cast<const uint4*>(back + (size_t)row * H + h)));
             }
-            uint4 pk;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) o2[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
-            *reinterpret_cast<uint4*>(out + (size_t)t * H + h) = pk;
+            *reinterpret_cast<uint4*>(out + (size_t)t * H + h) = pack8_bf16(acc);
         }
     }
 }

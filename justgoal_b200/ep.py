@@ -6,8 +6,8 @@ moe_common.cuh:14-15).  This module supplies the two exchanges around that share
 
   route own tokens -> DISPATCH (ONE all-to-all of packed rows: fp8 row + scales + the token's top-k
   ids/weights, one copy per (token, destination rank); b200moe_ep_pack / _unpack) -> local experts
-  (b200moe_forward_routed: bf16 row = sum over the local experts of a received token) -> COMBINE
-  (all-to-all of the bf16 partial rows back to the token's owner) -> b200moe_ep_combine: fp32 sum over
+  (b200moe_forward_routed: fp16 row = partial sum over the local experts of a received token) -> COMBINE
+  (all-to-all of the fp16 partial rows back to the token's owner) -> b200moe_ep_combine: fp32 sum over
   the destination ranks in rank order, one rounding to bf16.
 
 One process per GPU, `torch.distributed` (NCCL over NVLink) for the exchange.  The exchange logic
@@ -101,10 +101,10 @@ class CudaBackend:
         return self.layer.ep_unpack(wire)
 
     def experts(self, idx, w, hidden, hscale):
-        """bf16 [n, H]: per received token the sum over this rank's experts."""
+        """fp16 [n, H]: per received token the partial sum over this rank's experts."""
         return self.layer.forward_routed(idx, w, hidden, hscale, self.w["gemm1_weights"], self.w["gemm1_weights_scale"],
                                          self.w["gemm2_weights"], self.w["gemm2_weights_scale"], self.offset,
-                                         out_dtype=torch.bfloat16)
+                                         out_dtype=torch.float16)
 
     def combine(self, back, row_of, T):
         return self.layer.ep_combine(back, row_of, T)
@@ -114,7 +114,7 @@ class PeerExchange:
     """The exchange over peer memory (NVLink stores + flag barriers, csrc/ep_p2p.cuh) instead of NCCL
     all-to-alls: no host synchronisation and no library collective in a step.  One symmetric buffer per
     rank (torch symmetric memory supplies the mapping and the peer addresses; the kernels are this
-    library's): flags | status word | wire [world][cap] rows | back [world][cap][H] bf16."""
+    library's): flags | status word | wire [world][cap] rows | back [world][cap][H] fp16."""
 
     FLAGS_BYTES = 4096          # flags uint32[16] at 0, device status int at 1024
 
@@ -161,7 +161,7 @@ class PeerExchange:
         self.peer_back = arr(*[b + self.back_off for b in bases])
         self.status = self.buf[1024:1028].view(torch.int32)
         self.wire = self.buf[self.wire_off:self.wire_off + wire_bytes].view(self.world * self.cap, self.row_bytes)
-        self.back = self.buf[self.back_off:self.back_off + back_bytes].view(torch.bfloat16).view(
+        self.back = self.buf[self.back_off:self.back_off + back_bytes].view(torch.float16).view(
             self.world * self.cap, shape.hidden)
         self.flags = self.buf[:64].view(torch.int32)          # uint32[16] arrival flags, entry r written by rank r
         self.epoch = 0
@@ -202,7 +202,7 @@ class PeerExchange:
         return x, sc, idx, w
 
     def experts_to_peers(self, idx, w, hidden, hscale, weights, offset):
-        """The local experts over all wire slots; the last kernel stores every present slot's bf16 row straight
+        """The local experts over all wire slots; the last kernel stores every present slot's fp16 partial row straight
         into its owner's back slot (b200moe_forward_routed_slots: no intermediate buffer, no return copy)."""
         n = self.world * self.cap
         ws = self.layer.workspace(n)
@@ -295,13 +295,13 @@ class ExpertParallelMoE:
         wire = _a2a(wire, n_recv, plan.send_counts, plan.recv_counts, g)
         x_recv, sc_recv, idx_recv, w_recv = be.unpack(wire)
         mark("dispatch")
-        # LOCAL EXPERTS: sum over this rank's experts for every received token, as bf16 rows
+        # LOCAL EXPERTS: partial sum over this rank's experts for every received token, as fp16 rows
         if n_recv:
             part = be.experts(idx_recv, w_recv, x_recv, sc_recv)
         else:
-            part = torch.zeros(0, H, dtype=torch.bfloat16, device=hidden_states.device)
+            part = torch.zeros(0, H, dtype=torch.float16, device=hidden_states.device)
         mark("experts")
-        # COMBINE: bf16 partial rows back to the owners, fp32 sum over destination ranks, one rounding
+        # COMBINE: fp16 partial rows back to the owners, fp32 sum over destination ranks, one rounding
         back = _a2a(part, plan.send_token.numel(), plan.recv_counts, plan.send_counts, g)
         out = be.combine(back, plan.row_of, T)
         mark("combine")

@@ -141,13 +141,15 @@ class MoELayer:
     def forward_routed(self, topk_idx, topk_w, hidden_states, hidden_states_scale, gemm1_weights,
                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset, output=None,
                        out_dtype=torch.float32):
-        """Expert part only: the sum over the local experts, fp32 (no rounding) or bf16 rows."""
+        """Expert part only: the sum over the local experts as fp32 (no rounding), bf16, or fp16 rows (the form
+        partial rows travel in between the ranks of an expert-parallel layer)."""
         s = self.shape
         T = int(hidden_states.shape[0])
         if output is None:
             output = torch.empty(T, s.hidden, dtype=out_dtype, device=hidden_states.device)
-        if output.dtype not in (torch.float32, torch.bfloat16) or not output.is_contiguous():
-            raise ValueError("output must be a contiguous fp32 or bf16 [T, hidden] tensor")
+        kinds = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+        if output.dtype not in kinds or not output.is_contiguous():
+            raise ValueError("output must be a contiguous fp32, bf16 or fp16 [T, hidden] tensor")
         if T == 0:
             return output
         if topk_idx.dtype != torch.int32 or topk_w.dtype != torch.float32:
@@ -158,7 +160,7 @@ class MoELayer:
         stream = torch.cuda.current_stream(hidden_states.device).cuda_stream
         rc = _lib.lib.b200moe_forward_routed(self._h, *[_ptr(t) for t in tensors], T,
                                              _scalar(local_expert_offset, int), _ptr(output),
-                                             int(output.dtype == torch.bfloat16), _ptr(ws),
+                                             kinds[output.dtype], _ptr(ws),
                                              ws.numel(), C.c_void_p(stream))
         _lib.check(rc, "b200moe_forward_routed")
         return output
@@ -196,11 +198,11 @@ class MoELayer:
 
     def ep_combine(self, partial_rows, row_of, num_tokens):
         """Owner-rank side of the expert-parallel combine: bf16 [T, hidden] = per token the fp32 sum, in
-        rank order, of the bf16 rows `partial_rows[row_of[r, t]]` (row_of int32 [world, T], -1 = none)."""
+        rank order, of the fp16 partial rows `partial_rows[row_of[r, t]]` (row_of int32 [world, T], -1 = none)."""
         s = self.shape
         world = int(row_of.shape[0])
-        if partial_rows.dtype != torch.bfloat16 or row_of.dtype != torch.int32 or row_of.shape[1] != num_tokens:
-            raise ValueError("partial_rows must be bf16 [n, hidden] and row_of int32 [world, T]")
+        if partial_rows.dtype != torch.float16 or row_of.dtype != torch.int32 or row_of.shape[1] != num_tokens:
+            raise ValueError("partial_rows must be fp16 [n, hidden] and row_of int32 [world, T]")
         out = torch.empty(num_tokens, s.hidden, dtype=torch.bfloat16, device=partial_rows.device)
         stream = torch.cuda.current_stream(partial_rows.device).cuda_stream
         rc = _lib.lib.b200moe_ep_combine(self._h, _ptr(_contig(partial_rows)), _ptr(_contig(row_of)), world,

@@ -80,9 +80,9 @@ class EmulatedRanks:
                                                            self.weights[r]["gemm1_weights_scale"],
                                                            self.weights[r]["gemm2_weights"],
                                                            self.weights[r]["gemm2_weights_scale"], self.offset(r),
-                                                           out_dtype=torch.bfloat16))
+                                                           out_dtype=torch.float16))
             else:
-                parts.append(torch.zeros(0, self.shape.hidden, dtype=torch.bfloat16, device="cuda"))
+                parts.append(torch.zeros(0, self.shape.hidden, dtype=torch.float16, device="cuda"))
         outs = []
         for q in range(W):                                             # combine: rows come back in send order
             back = []

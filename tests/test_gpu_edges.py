@@ -105,7 +105,7 @@ def test_workspace_reuse_across_sizes():
 
 
 def test_ep_combine_kernel_matches_restatement():
-    """b200moe_ep_combine: fp32 sum in rank order of the bf16 rows a token's ranks sent back."""
+    """b200moe_ep_combine: fp32 sum in rank order of the fp16 partial rows a token's ranks sent back."""
     from justgoal_b200 import MoELayer
     shape = I.TINY_DS
     layer = MoELayer(shape)
@@ -115,7 +115,7 @@ def test_ep_combine_kernel_matches_restatement():
     has[:, 5] = False                                     # a token nobody computed: zeros
     row_of = torch.full((world, T), -1, dtype=torch.int32)
     row_of[has] = torch.arange(int(has.sum()), dtype=torch.int32)
-    back = torch.randn(int(has.sum()), H, generator=g).to(torch.bfloat16)
+    back = torch.randn(int(has.sum()), H, generator=g).to(torch.float16)
     got = layer.ep_combine(back.cuda(), row_of.cuda(), T).cpu()
     want = torch.zeros(T, H, dtype=torch.float32)
     for r in range(world):
@@ -125,7 +125,7 @@ def test_ep_combine_kernel_matches_restatement():
     assert bool((got[5].float() == 0).all())
 
 
-def test_forward_routed_bf16_is_the_rounded_fp32_result():
+def test_forward_routed_bf16_and_fp16_are_the_rounded_fp32_result():
     from justgoal_b200 import MoELayer
     shape = I.TINY_DS
     T = 45
@@ -135,9 +135,11 @@ def test_forward_routed_bf16_is_the_rounded_fp32_result():
     args = (idx, w, d["hidden_states"], d["hidden_states_scale"], d["gemm1_weights"], d["gemm1_weights_scale"],
             d["gemm2_weights"], d["gemm2_weights_scale"], d["local_expert_offset"])
     f32 = layer.forward_routed(*args).clone()
-    b16 = layer.forward_routed(*args, out_dtype=torch.bfloat16)
+    b16 = layer.forward_routed(*args, out_dtype=torch.bfloat16).clone()
+    h16 = layer.forward_routed(*args, out_dtype=torch.float16)
     torch.cuda.synchronize()
     assert torch.equal(b16.view(torch.int16), f32.to(torch.bfloat16).view(torch.int16))
+    assert torch.equal(h16.view(torch.int16), f32.to(torch.float16).view(torch.int16))
 
 
 def test_ep_pack_unpack_round_trip():
