@@ -76,7 +76,7 @@ typedef struct b200moe_ws_layout {
     size_t act_hi;        /* uint8[rows_cap, I] e4m3 of SwiGLU output / scale              */
     size_t act_lo;        /* uint8[rows_cap, I] e4m3 of the rounding residual              */
     size_t act_scale;     /* float[I/128, rows_cap]                                        */
-    size_t y;             /* float[rows_cap, H] weighted expert outputs per row            */
+    size_t y;             /* fp16[rows_cap, H] weighted expert outputs per row             */
     size_t sk_count;      /* int32[2][4*SMs] arrival counters of K-split units (GEMM1, GEMM2)*/
     size_t slices;        /* int32[ceil(T*top_k/1024)][E_local] histogram of the local experts per
                              slice of 1024 (token, expert) pairs, token-major                */
@@ -136,7 +136,7 @@ int b200moe_route(b200moe_handle h, const void* routing_logits, const void* rout
 
 /* The expert part alone, for tokens that were routed elsewhere (expert-parallel receive
  * side): like b200moe_forward but takes topk_idx/topk_w instead of logits, and writes the
- * sum over the LOCAL experts to output [T, H]: output_kind 0 = fp32 (no rounding), 1 = bf16
+ * sum over the LOCAL experts to output [T, H]: output_kind 0 = fp32 (the sum unrounded), 1 = bf16
  * (the operator's output type: right when the local experts are all of a token's experts),
  * 2 = fp16, the form PARTIAL rows travel in between ranks (two bytes like bf16 but 11
  * significant bits: the owner adds the partial rows of up to world ranks in fp32 before the

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libb200moe.so")
+# B200MOE_LIB selects another build of the library (A/B timing of kernel variants); default: the in-tree build
+LIB_PATH = os.environ.get("B200MOE_LIB") or os.path.join(HERE, "libb200moe.so")
 
 
 class Config(C.Structure):

@@ -19,6 +19,7 @@
 #include "front.cuh"
 #include "ep_p2p.cuh"
 #include "gemm.cuh"
+#include "gemm_pair.cuh"
 #include "permute.cuh"
 #include "quant.cuh"
 #include "routing.cuh"
@@ -36,6 +37,7 @@ struct b200moe_ctx {
     cudaEvent_t* prof_events;  // [prof_slots][PROF_POINTS]
     int ablate;                // B200MOE_ABLATE environment variable at create (timing experiments; 0 in normal use)
     unsigned long long wait_limit_ns;   // limit of the waits on a PEER (barrier flags); b200moe_set_wait_limit_ns
+    int pair_grid[2];          // CTAs of the SM-pair kernels (GEMM1, GEMM2): 2 x clusters that can be resident; 0 = unusable
 };
 
 namespace {
@@ -154,7 +156,7 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     L->act_hi = take(rows * c.intermediate);
     L->act_lo = take(rows * c.intermediate);
     L->act_scale = take((size_t)(c.intermediate / 128) * rows * 4);
-    L->y = take(rows * c.hidden * 4);
+    L->y = take(rows * c.hidden * 2);
     L->sk_partial = take((size_t)2 * h->num_sms * SK_SLOT_FLOATS_MAX * 4);
     L->trace = take((size_t)2 * h->num_sms * TRACE_SLOTS * 8 + 2 * 8 * KLOG_N * 8);   // [GEMM1 | GEMM2][CTA][slot], then K-block logs
     L->rows_cap = rows;
@@ -191,6 +193,59 @@ cudaError_t launch_gemm_ntok(int ntok, int grid, cudaStream_t st, const CUtensor
         case 64: return launch_gemm<64, G1>(grid, st, w, b0, b1, p);
         default: return launch_gemm<128, G1>(grid, st, w, b0, b1, p);
     }
+}
+
+// SM-pair kernels (gemm_pair.cuh): clusters of two CTAs.  The grid is twice the number of clusters the device
+// can hold at once (a persistent kernel with a static schedule must not queue a cluster behind another one).
+template <bool G1>
+cudaError_t launch_cfg_pair(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int grid, cudaStream_t st, bool pdl) {
+    cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(PairCfg<G1>::NTHREADS);
+    cfg.dynamicSmemBytes = PairCfg<G1>::SMEM_BYTES; cfg.stream = st;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 2 : 1;
+    return cudaSuccess;
+}
+
+template <bool G1>
+int set_attr_pair(int num_sms, int* grid_out) {
+    using C = PairCfg<G1>;
+    *grid_out = 0;
+    cudaFuncAttributes fa;
+    cudaError_t e = cudaFuncGetAttributes(&fa, gemm_pair_kernel<G1>);
+    if (e != cudaSuccess) return (int)e;
+    if (fa.numRegs != C::LAUNCH_REGS) return B200MOE_E_BUILD;
+    e = cudaFuncSetAttribute(gemm_pair_kernel<G1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[2];
+    launch_cfg_pair<G1>(cfg, attr, (num_sms / 2) * 2, nullptr, false);
+    int clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&clusters, gemm_pair_kernel<G1>, &cfg);
+    if (e != cudaSuccess) { cudaGetLastError(); return 0; }       // pairs unusable on this device: single-SM kernels run
+    if (clusters > num_sms / 2) clusters = num_sms / 2;
+    *grid_out = clusters * 2;
+    return 0;
+}
+
+template <bool G1>
+cudaError_t launch_gemm_pair(int grid, cudaStream_t st, const CUtensorMap& w, const CUtensorMap& b0, const CUtensorMap& b1,
+                             const GemmParams& p) {
+    cudaLaunchConfig_t cfg; cudaLaunchAttribute attr[2];
+    launch_cfg_pair<G1>(cfg, attr, grid, st, (g_call_pdl & (G1 ? PDL_GEMM1 : PDL_GEMM2)) != 0);
+    return cudaLaunchKernelEx(&cfg, gemm_pair_kernel<G1>, w, b0, b1, p);
+}
+
+// Full token tiles run on SM pairs when B200MOE_PAIR=1.  Off by default: measured on B200, both families run
+// into the 1 kW power cap within milliseconds, and at the clocks the cap leaves (~1.45-1.55 GHz) the pair
+// kernels are 8 % (GEMM1) / 0 % (GEMM2) slower than the single-SM ones although they need fewer cycles per
+// 128-K block at full clock (1008 against 1180).
+bool use_pairs(const b200moe_ctx* h, int ntok) {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("B200MOE_PAIR"); v = e ? atoi(e) : 0; }
+    return v != 0 && ntok == 128 && h->pair_grid[0] >= 2 && h->pair_grid[1] >= 2;
 }
 
 bool cfg_ok(const b200moe_config& c) {
@@ -271,10 +326,11 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     uint8_t* act_hi = ws + L.act_hi;
     uint8_t* act_lo = ws + L.act_lo;
     float* act_scale = reinterpret_cast<float*>(ws + L.act_scale);
-    float* y = reinterpret_cast<float*>(ws + L.y);
+    __half* y = reinterpret_cast<__half*>(ws + L.y);
 
     CUtensorMap m_w13, m_w2, m_a, m_hi, m_lo;
     int rc;
+    const bool pairs = use_pairs(h, ntok);
     if ((rc = make_map(&m_w13, w13, (uint64_t)El * 2 * I, H, 128))) return rc;
     if ((rc = make_map(&m_w2, w2, (uint64_t)El * H, I, 128))) return rc;
     if ((rc = make_map(&m_a, a_perm, rows_cap, H, ntok))) return rc;
@@ -325,7 +381,8 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g1.ablate = h->ablate & 0xFF;
     g1.trace = reinterpret_cast<long long*>(ws + L.trace);
     g1.klog = g1.trace + (size_t)2 * h->num_sms * TRACE_SLOTS;
-    CU_TRY(launch_gemm_ntok<true>(ntok, h->num_sms, st, m_w13, m_a, m_a, g1));
+    if (pairs) CU_TRY(launch_gemm_pair<true>(h->pair_grid[0], st, m_w13, m_a, m_a, g1));
+    else CU_TRY(launch_gemm_ntok<true>(ntok, h->num_sms, st, m_w13, m_a, m_a, g1));
     CU_TRY(prof_mark(h, 4, st));
 
     GemmParams g2;
@@ -341,7 +398,8 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g2.ablate = (h->ablate >> 8) & 0xFF;
     g2.trace = g1.trace + (size_t)h->num_sms * TRACE_SLOTS;
     g2.klog = g1.klog + 8 * KLOG_N;
-    CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
+    if (pairs) CU_TRY(launch_gemm_pair<false>(h->pair_grid[1], st, m_w2, m_hi, m_lo, g2));
+    else CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
     CU_TRY(prof_mark(h, 5, st));
 
     const int cgrid = T < h->num_sms * 8 ? T : h->num_sms * 8;
@@ -349,13 +407,13 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     memset(&so, 0, sizeof(so));            // cap == 0: rows go to `out`
     if (slot_out) so = *slot_out;
     if (out_kind == OUT_BF16)
-        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_BF16>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_BF16>, dim3(cgrid), dim3(256), 0, st, (const __half*)y, topk_idx,
                         (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
     else if (out_kind == OUT_F16)
-        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F16>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F16>, dim3(cgrid), dim3(256), 0, st, (const __half*)y, topk_idx,
                         (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
     else
-        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F32>, dim3(cgrid), dim3(256), 0, st, (const float*)y, topk_idx,
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F32>, dim3(cgrid), dim3(256), 0, st, (const __half*)y, topk_idx,
                         (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
     CU_TRY(prof_mark(h, 6, st));
     if (h->prof_slots) ++h->prof_calls;
@@ -412,6 +470,11 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     h->cfg = *cfg; h->device = dev; h->num_sms = sms;
     h->prof_slots = 0; h->prof_calls = 0; h->prof_events = nullptr;
     h->wait_limit_ns = WAIT_LIMIT_NS;
+    int rc_p;
+    if ((rc_p = set_attr_pair<true>(sms, &h->pair_grid[0])) || (rc_p = set_attr_pair<false>(sms, &h->pair_grid[1]))) {
+        delete h;
+        return rc_p;
+    }
 #ifdef B200MOE_ENABLE_ABLATE
     const char* ab = getenv("B200MOE_ABLATE");
     h->ablate = ab ? atoi(ab) : 0;

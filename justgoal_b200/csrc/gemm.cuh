@@ -53,7 +53,7 @@ struct GemmParams {
     const float* b_scale; // [KB, rows_cap] token-side scales
     int rows_cap;
     uint8_t* act_hi; uint8_t* act_lo; float* act_scale; int I;   // GEMM1 outputs
-    const float* row_w; float* y; int H;                          // GEMM2 outputs
+    const float* row_w; __half* y; int H;                         // GEMM2 outputs: y[row, h] = row_w[row] * O[row, h] as fp16
     int evict_first_weights;
     int* sk_count;        // [4 * gridDim.x] arrival counters of split units (zero at launch)
     float* sk_partial;    // [2 * gridDim.x] slots of SLOT_FLOATS floats
@@ -201,6 +201,23 @@ struct SkIter {
 };
 
 __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+// N consecutive columns of one weighted output row, rounded to fp16 (the per-pair rows the combine adds up in
+// fp32), as 32-byte stores
+template <int N>
+__device__ __forceinline__ void store_y_row(__half* dst, const float* acc, float w) {
+    static_assert(N % 16 == 0, "16 columns per store");
+#pragma unroll
+    for (int i = 0; i < N; i += 16) {
+        uint32_t pk[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const __half2 h = __floats2half2_rn(acc[i + 2 * j] * w, acc[i + 2 * j + 1] * w);
+            pk[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        st_global_v8(dst + i, pk[0], pk[1], pk[2], pk[3], pk[4], pk[5], pk[6], pk[7]);
+    }
+}
 
 template <int N>
 __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, float* v) {
@@ -811,22 +828,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 }
             } else if (C::TOK_ON_M) {
                 // 64 consecutive output columns of this thread's row per accumulator, as 256-bit stores.
-                // The 128 KB of a unit drain at ~32 B per cycle per SM (~2 us) whatever the pattern: a
-                // shuffle transpose that made every lane quad write 128 contiguous bytes was measured equal.
+                // A unit's rows drain at ~32 B per cycle per SM whatever the pattern (a shuffle transpose that
+                // made every lane quad write 128 contiguous bytes was measured equal), so they leave as fp16.
                 if (m < un.nvalid) {
                     const size_t row = (size_t)(un.row0 + m);
 #pragma unroll
                     for (int a = 0; a < C::NACCUM; ++a) {
                         const int col0 = un.mt * p.unit_rows + a * p.gate_offset + c0;
-                        if (col0 < p.valid_rows) {
-                            float* dst = p.y + row * p.H + col0;
-#pragma unroll
-                            for (int i = 0; i < C::NC; i += 8)
-                                st_global_v8(dst + i, __float_as_uint(acc[a][i] * wrow), __float_as_uint(acc[a][i + 1] * wrow),
-                                             __float_as_uint(acc[a][i + 2] * wrow), __float_as_uint(acc[a][i + 3] * wrow),
-                                             __float_as_uint(acc[a][i + 4] * wrow), __float_as_uint(acc[a][i + 5] * wrow),
-                                             __float_as_uint(acc[a][i + 6] * wrow), __float_as_uint(acc[a][i + 7] * wrow));
-                        }
+                        if (col0 < p.valid_rows) store_y_row<C::NC>(p.y + row * p.H + col0, acc[a], wrow);
                     }
                 }
             } else if (G1) {
@@ -878,8 +887,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     if (c < un.nvalid) {
                         const size_t row = (size_t)(un.row0 + c);
                         const float w = __ldg(p.row_w + row);
-                        p.y[row * p.H + col0] = acc[0][i] * w;
-                        if (second) p.y[row * p.H + col0 + p.gate_offset] = acc[1][i] * w;
+                        p.y[row * p.H + col0] = __float2half_rn(acc[0][i] * w);
+                        if (second) p.y[row * p.H + col0 + p.gate_offset] = __float2half_rn(acc[1][i] * w);
                     }
                 }
             }

@@ -196,8 +196,9 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__
     }
 }
 
-// y holds fp32 rows (bf16 rows were tried: halves this kernel's traffic, but the extra rounding of
-// up to eight partial rows pushed 1 element in 6.4 million over the 1e-2 / 1e-2 tolerance).
+// y holds one fp16 row per (token, expert) pair: 11 significant bits, half the traffic of fp32 rows in the
+// GEMM2 epilogue and here (bf16 rows - 8 bits - were tried first: the extra rounding of up to eight rows pushed
+// 1 element in 6.4 million over the 1e-2 / 1e-2 tolerance; fp16's error is an eighth of that).
 // out[t, :] = sum over the token's local pairs (ascending expert order = the order they were
 // placed in topk rows is NOT sorted, so sort the <= 8 rows by row index, which is expert
 // order) of y[row, :]; fp32 accumulation, one rounding.  Tokens without a local pair get zeros.
@@ -239,7 +240,7 @@ __device__ __forceinline__ void add8_f16(float* acc, const uint4& v) {
 }
 
 template <int OUT>
-__global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ topk_idx,
+__global__ void __launch_bounds__(256) combine_kernel(const __half* __restrict__ y, const int32_t* __restrict__ topk_idx,
                                                       const int32_t* __restrict__ pair_row, void* __restrict__ out,
                                                       int T, int H, int top_k, int local_offset, int num_local,
                                                       const SlotOut slots) {
@@ -276,13 +277,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const float* __restrict__ 
         const int n = s_n;
         for (int h = threadIdx.x * 8; h < H; h += blockDim.x * 8) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int j = 0; j < n; ++j) {
-                const float* src = y + (size_t)s_rows[j] * H + h;
-                const float4 a = *reinterpret_cast<const float4*>(src);
-                const float4 b = *reinterpret_cast<const float4*>(src + 4);
-                acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
-                acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
-            }
+            for (int j = 0; j < n; ++j) add8_f16(acc, *reinterpret_cast<const uint4*>(y + (size_t)s_rows[j] * H + h));
             if (OUT == OUT_BF16) {
                 *reinterpret_cast<uint4*>(out_row + h) = pack8_bf16(acc);
             } else if (OUT == OUT_F16) {

@@ -22,7 +22,7 @@ import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SOURCES = ["b200moe.cu", "b200moe.h", "common.cuh", "routing.cuh", "permute.cuh", "front.cuh", "ep_p2p.cuh",
-            "gemm.cuh", "quant.cuh"]
+            "gemm.cuh", "gemm_pair.cuh", "quant.cuh"]
 _LOCK = threading.Lock()
 _LIB = None
 _HANDLES = {}       # (H, I, E, E_local, device index) -> handle

@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 DEFINITION = "moe_fp8_block_scale_ds_routing_topk8_ng8_kg4_e32_h7168_i2048"
-CSRC = ["b200moe.cu", "common.cuh", "routing.cuh", "permute.cuh", "front.cuh", "ep_p2p.cuh", "gemm.cuh", "quant.cuh"]
+CSRC = ["b200moe.cu", "common.cuh", "routing.cuh", "permute.cuh", "front.cuh", "ep_p2p.cuh", "gemm.cuh", "gemm_pair.cuh", "quant.cuh"]
 
 
 def sources():

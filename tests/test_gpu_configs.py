@@ -141,3 +141,39 @@ def test_ep_share_qwen3_shape():
     """Qwen3-MoE shape (hidden 4096, intermediate 1536, 128 experts, 16 per rank, softmax top-8,
     renormalised, no groups), one rank's share of the 8-GPU configuration at its full T=2048."""
     _share_check(I.QWEN3_MOE, 2048, 48, 1.0, seed=22)
+
+
+def test_sm_pair_kernels_match_the_single_sm_kernels():
+    """The cta_group::2 family (B200MOE_PAIR=1: two CTAs of a cluster share every weight tile) computes the same
+    arithmetic as the default single-SM family: same bits.  Run in a child process because the switch is read
+    once per process."""
+    import os
+    import subprocess
+    import sys
+    code = r"""
+import sys, torch
+sys.path.insert(0, %r); sys.path.insert(0, %r)
+import util
+from util import I
+from justgoal_b200 import MoELayer
+outs = []
+for shape, T, seed in ((I.TINY_RENORM, 700, 31), (I.TINY_DS, 2000, 5)):
+    d = I.make_inputs(shape, T, seed=seed)
+    layer = MoELayer(shape)
+    out = layer.forward(*util.op_args(util.to_cuda(d)))
+    torch.cuda.synchronize()
+    assert layer.status(T) == 0 and int(layer.layout(T).token_tile) == 128
+    outs.append(out.cpu())
+torch.save(outs, sys.argv[1])
+""" % (util.ROOT, os.path.join(util.ROOT, "tests"))
+    import tempfile
+    res = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        for pair in ("0", "1"):
+            path = os.path.join(tmp, f"out{pair}.pt")
+            env = dict(os.environ, B200MOE_PAIR=pair)
+            r = subprocess.run([sys.executable, "-c", code, path], env=env, capture_output=True, text=True, timeout=600)
+            assert r.returncode == 0, r.stderr[-2000:]
+            res[pair] = torch.load(path)
+    for a, b in zip(res["0"], res["1"]):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
