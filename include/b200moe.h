@@ -76,7 +76,7 @@ typedef struct b200moe_ws_layout {
     size_t act_hi;        /* uint8[rows_cap, I] e4m3 of SwiGLU output / scale              */
     size_t act_lo;        /* uint8[rows_cap, I] e4m3 of the rounding residual              */
     size_t act_scale;     /* float[I/128, rows_cap]                                        */
-    size_t y;             /* fp16[rows_cap, H] weighted expert outputs per row             */
+    size_t y;             /* fp16[rows_cap, H] expert output per row (before the weight)   */
     size_t sk_count;      /* int32[2][4*SMs] arrival counters of K-split units (GEMM1, GEMM2)*/
     size_t slices;        /* int32[ceil(T*top_k/1024)][E_local] histogram of the local experts per
                              slice of 1024 (token, expert) pairs, token-major                */
@@ -196,10 +196,12 @@ int b200moe_ep_unpack_slots(b200moe_handle h, const void* wire, int n_slots, voi
                             void* cuda_stream);
 int b200moe_ep_return(b200moe_handle h, const void* partial_rows_fp16, const int32_t* topk_idx_slots,
                       int cap, int world, int my_rank, void* const* peer_back, void* cuda_stream);
-/* b200moe_forward_routed over the world*cap slots with b200moe_ep_return folded into its last kernel:
- * the combine stores every present slot's fp16 partial row straight into the owner's back slot. */
-int b200moe_forward_routed_slots(b200moe_handle h, const int32_t* topk_idx, const float* topk_w,
-                                 const void* hidden_states, const void* hidden_states_scale,
+/* The local experts over the world*cap wire slots, read IN PLACE (no unpack copy: ids, weights, fp8 rows and
+ * scales are taken from the packed rows the peers stored; absent slots carry ids -1), with b200moe_ep_return
+ * folded into the last kernel: every present slot's fp16 partial row is stored straight into the owner's back
+ * slot.  `wire` = this rank's [world][cap] dispatch rows (16-byte aligned).  Replaces the sequence
+ * b200moe_ep_unpack_slots -> b200moe_forward_routed -> b200moe_ep_return of a step. */
+int b200moe_forward_routed_slots(b200moe_handle h, const void* wire,
                                  const void* gemm1_weights, const void* gemm1_weights_scale,
                                  const void* gemm2_weights, const void* gemm2_weights_scale,
                                  int cap, int world, int my_rank, int local_expert_offset,

@@ -48,7 +48,7 @@ def _load():
     lib.b200moe_ep_unpack_slots.argtypes = [vp, vp, i, vp, vp, vp, vp, vp]
     lib.b200moe_ep_return.argtypes = [vp, vp, vp, i, i, i, pv, vp]
     lib.b200moe_ep_combine_slots.argtypes = [vp, vp, vp, i, i, i, vp, vp]
-    lib.b200moe_forward_routed_slots.argtypes = [vp, vp, vp] + [vp] * 6 + [i, i, i, i, pv, vp, sz, vp]
+    lib.b200moe_forward_routed_slots.argtypes = [vp, vp] + [vp] * 4 + [i, i, i, i, pv, vp, sz, vp]
     lib.b200moe_ep_pack.argtypes = [vp, vp, vp, vp, vp, vp, i, i, vp, vp]
     lib.b200moe_ep_unpack.argtypes = [vp, vp, i, vp, vp, vp, vp, vp]
     lib.b200moe_set_wait_limit_ns.argtypes = [vp, C.c_ulonglong]

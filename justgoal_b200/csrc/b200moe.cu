@@ -310,7 +310,9 @@ inline cudaError_t prof_mark(b200moe_ctx* h, int point, cudaStream_t st) {
 int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
                 const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2, int T,
                 int local_offset, void* out, int out_kind, uint8_t* ws, const b200moe_ws_layout& L, cudaStream_t st,
-                bool fused_front = false, const SlotOut* slot_out = nullptr) {
+                bool fused_front = false, const SlotOut* slot_out = nullptr, int wire_pitch = 0) {
+    // wire_pitch > 0: the tokens are packed dispatch rows read in place - `hidden` points at the first row,
+    // topk_idx / topk_w at the ids / weights inside it, rows are wire_pitch bytes apart, hidden_scale is unused
     const b200moe_config& c = h->cfg;
     const int El = c.num_local_experts, H = c.hidden, I = c.intermediate;
     const int ntok = (int)L.token_tile, rows_cap = (int)L.rows_cap;
@@ -340,6 +342,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     PlanParams pp;
     pp.T = T; pp.top_k = c.top_k; pp.num_local = El; pp.local_offset = local_offset; pp.token_tile = ntok;
     pp.topk_idx = topk_idx; pp.topk_w = topk_w; pp.status = status; pp.counts = counts;
+    pp.pair_stride = wire_pitch > 0 ? wire_pitch / 4 : c.top_k;
     pp.slices = reinterpret_cast<const int*>(ws + L.slices);
     pp.expert_row0 = row0; pp.tile_prefix = tiles; pp.pair_row = pair_row; pp.row_token = row_token;
     pp.row_w = row_w; pp.rows_cap = rows_cap;
@@ -361,8 +364,9 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
         int ggrid = (int)((max_rows + 7) / 8);
         if (ggrid > h->num_sms * 8) ggrid = h->num_sms * 8;
         CU_TRY(launch_k(PDL_GATHER, gather_kernel, dim3(ggrid), dim3(256), 0, st, static_cast<const uint8_t*>(hidden),
-                        static_cast<const float*>(hidden_scale), (const int32_t*)row_token, (const int*)status, a_perm,
-                        a_scale, T, H, rows_cap));
+                        wire_pitch > 0 ? (const float*)nullptr : static_cast<const float*>(hidden_scale),
+                        (const int32_t*)row_token, (const int*)status, a_perm, a_scale, T, H, rows_cap,
+                        wire_pitch > 0 ? wire_pitch : H));
         CU_TRY(prof_mark(h, 3, st));
     }
 
@@ -408,13 +412,13 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     if (slot_out) so = *slot_out;
     if (out_kind == OUT_BF16)
         CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_BF16>, dim3(cgrid), dim3(256), 0, st, (const __half*)y, topk_idx,
-                        (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
+                        (const int32_t*)pair_row, (const float*)row_w, out, T, H, c.top_k, pp.pair_stride, local_offset, El, so));
     else if (out_kind == OUT_F16)
         CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F16>, dim3(cgrid), dim3(256), 0, st, (const __half*)y, topk_idx,
-                        (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
+                        (const int32_t*)pair_row, (const float*)row_w, out, T, H, c.top_k, pp.pair_stride, local_offset, El, so));
     else
         CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F32>, dim3(cgrid), dim3(256), 0, st, (const __half*)y, topk_idx,
-                        (const int32_t*)pair_row, out, T, H, c.top_k, local_offset, El, so));
+                        (const int32_t*)pair_row, (const float*)row_w, out, T, H, c.top_k, pp.pair_stride, local_offset, El, so));
     CU_TRY(prof_mark(h, 6, st));
     if (h->prof_slots) ++h->prof_calls;
     return 0;
@@ -611,7 +615,7 @@ int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const floa
     const int n = T * c.top_k;
     int grid = (n + 255) / 256;
     if (grid > h->num_sms * 4) grid = h->num_sms * 4;
-    count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, local_offset, c.num_local_experts,
+    count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, c.top_k, c.top_k, local_offset, c.num_local_experts,
                                        reinterpret_cast<int*>(ws + L.slices));
     CU_TRY(cudaGetLastError());
     CU_TRY(prof_mark(h, 1, st));
@@ -716,15 +720,14 @@ int b200moe_ep_return(b200moe_handle h, const void* partial_rows, const int32_t*
     return 0;
 }
 
-int b200moe_forward_routed_slots(b200moe_handle h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
-                                 const void* hidden_scale, const void* w13, const void* s13, const void* w2,
+int b200moe_forward_routed_slots(b200moe_handle h, const void* wire, const void* w13, const void* s13, const void* w2,
                                  const void* s2, int cap, int world, int my_rank, int local_offset,
                                  void* const* peer_back, void* workspace, size_t workspace_bytes, void* stream) {
     SlotOut so;
     if (!h || cap < 1 || my_rank < 0 || my_rank >= world || !fill_peers(so.back, peer_back, world) ||
-        (long long)cap * world > 0x7FFFFFFF)
+        (long long)cap * world > 0x7FFFFFFF || h->cfg.top_k > 32)
         return B200MOE_E_BADARG;
-    if (!topk_idx || !topk_w || !hidden || !hidden_scale || !w13 || !s13 || !w2 || !s2) return B200MOE_E_BADARG;
+    if (!wire || !w13 || !s13 || !w2 || !s2 || (reinterpret_cast<uintptr_t>(wire) & 15)) return B200MOE_E_BADARG;
     so.cap = cap; so.my_rank = my_rank;
     const int T = cap * world;
     b200moe_ws_layout L;
@@ -733,19 +736,24 @@ int b200moe_forward_routed_slots(b200moe_handle h, const int32_t* topk_idx, cons
     const b200moe_config& c = h->cfg;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
+    // the slots are read where the peers stored them: fp8 row | scales | ids | weights, one row per slot
+    const int pitch = ep_row_bytes(c.hidden, c.top_k);
+    const uint8_t* rows = static_cast<const uint8_t*>(wire);
+    const int32_t* ids = reinterpret_cast<const int32_t*>(rows + c.hidden + 4 * (c.hidden >> 7));
+    const float* wts = reinterpret_cast<const float*>(rows + c.hidden + 4 * (c.hidden >> 7) + 4 * c.top_k);
     set_call_pdl(T);
     CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
     CU_TRY(prof_mark(h, 0, st));
     const int n = T * c.top_k;
     int grid = (n + 255) / 256;
     if (grid > h->num_sms * 4) grid = h->num_sms * 4;
-    count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, local_offset, c.num_local_experts,
+    count_kernel<<<grid, 256, 0, st>>>(ids, n, c.top_k, pitch / 4, local_offset, c.num_local_experts,
                                        reinterpret_cast<int*>(ws + L.slices));
     CU_TRY(cudaGetLastError());
     CU_TRY(prof_mark(h, 1, st));
     // the rows leave through the peer slots; `out` is never dereferenced in that mode
-    return run_experts(h, topk_idx, topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, ws, OUT_F16, ws, L, st,
-                       false, &so);
+    return run_experts(h, ids, wts, rows, nullptr, w13, s13, w2, s2, T, local_offset, ws, OUT_F16, ws, L, st,
+                       false, &so, pitch);
 }
 
 int b200moe_ep_combine_slots(b200moe_handle h, const void* back, const int32_t* topk_idx, int T, int cap, int world,
@@ -810,13 +818,14 @@ int b200moe_permute_noalloc(b200moe_handle h, const int32_t* topk_idx, const flo
         const int n = T * c.top_k;
         int grid = (n + 255) / 256;
         if (grid > h->num_sms * 4) grid = h->num_sms * 4;
-        count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, local_offset, El, reinterpret_cast<int*>(scratch + NOALLOC_HEAD_BYTES));
+        count_kernel<<<grid, 256, 0, st>>>(topk_idx, n, c.top_k, c.top_k, local_offset, El,
+                                           reinterpret_cast<int*>(scratch + NOALLOC_HEAD_BYTES));
         CU_TRY(cudaGetLastError());
     }
     PlanParams pp;
     pp.T = T; pp.top_k = c.top_k; pp.num_local = El; pp.local_offset = local_offset;
     pp.token_tile = pick_token_tile(c, T);
-    pp.topk_idx = topk_idx; pp.topk_w = topk_w;
+    pp.topk_idx = topk_idx; pp.topk_w = topk_w; pp.pair_stride = c.top_k;
     pp.status = reinterpret_cast<int*>(scratch);
     pp.counts = reinterpret_cast<int*>(scratch + 256);
     pp.tile_prefix = reinterpret_cast<int*>(scratch + 1536);

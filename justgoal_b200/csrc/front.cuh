@@ -47,9 +47,11 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_small_kernel(const Fro
 
     // ---- the routing result of all tokens, and the histogram of the local experts
     for (int i = tid; i < n; i += blockDim.x) {
-        const int id = pp.topk_idx[i];
+        const int tok = i / K;
+        const size_t src = (size_t)tok * pp.pair_stride + (i - tok * K);
+        const int id = pp.topk_idx[src];
         s_idx[i] = id;
-        s_w[i] = pp.topk_w[i];
+        s_w[i] = pp.topk_w[src];
         const int le = id - pp.local_offset;
         if (le >= 0 && le < El) atomicAdd(&s_cnt[le], 1);
     }

@@ -6,7 +6,7 @@
 //               epilogue: c = silu(gate) * up, per-(row, 128 columns) amax -> scale = amax/448,
 //               stored as TWO e4m3 values hi = rn(c/scale), lo = rn(c/scale - hi) under one scale.
 //   GEMM2 (G2): D[128, NTOK] = W2[e, mt*128 .. +128, :] . (act_hi + act_lo)[rows]^T, two MMAs per
-//               K step into the same accumulator; epilogue: y[row, h] = row_w[row] * D.
+//               K step into the same accumulator; epilogue: y[row, h] = D as fp16 (weighted by the combine).
 // Block scales change every 128 K, so each 128-K block is accumulated into a fresh TMEM region
 // and promoted into fp32 registers: acc += part * (token_scale[kb] * weight_scale[kb]).
 // The same arithmetic is stated by the reference's tcgen05 kernels
@@ -53,7 +53,8 @@ struct GemmParams {
     const float* b_scale; // [KB, rows_cap] token-side scales
     int rows_cap;
     uint8_t* act_hi; uint8_t* act_lo; float* act_scale; int I;   // GEMM1 outputs
-    const float* row_w; __half* y; int H;                         // GEMM2 outputs: y[row, h] = row_w[row] * O[row, h] as fp16
+    const float* row_w; __half* y; int H;                         // GEMM2 output: y[row, h] = O[row, h] as fp16 (the routing
+                                                                  // weight is applied by the combine, in fp32)
     int evict_first_weights;
     int* sk_count;        // [4 * gridDim.x] arrival counters of split units (zero at launch)
     float* sk_partial;    // [2 * gridDim.x] slots of SLOT_FLOATS floats
@@ -202,17 +203,17 @@ struct SkIter {
 
 __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
-// N consecutive columns of one weighted output row, rounded to fp16 (the per-pair rows the combine adds up in
-// fp32), as 32-byte stores
+// N consecutive columns of one expert-output row, rounded to fp16 (the per-pair rows the combine weighs and adds
+// up in fp32), as 32-byte stores
 template <int N>
-__device__ __forceinline__ void store_y_row(__half* dst, const float* acc, float w) {
+__device__ __forceinline__ void store_y_row(__half* dst, const float* acc) {
     static_assert(N % 16 == 0, "16 columns per store");
 #pragma unroll
     for (int i = 0; i < N; i += 16) {
         uint32_t pk[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const __half2 h = __floats2half2_rn(acc[i + 2 * j] * w, acc[i + 2 * j + 1] * w);
+            const __half2 h = __floats2half2_rn(acc[i + 2 * j], acc[i + 2 * j + 1]);
             pk[j] = *reinterpret_cast<const uint32_t*>(&h);
         }
         st_global_v8(dst + i, pk[0], pk[1], pk[2], pk[3], pk[4], pk[5], pk[6], pk[7]);
@@ -546,8 +547,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             // tokens-on-M: this thread's token scale, also one K block ahead (KPB == 1 there)
             const float* tsp = p.b_scale + (size_t)un.row0 + m;
             float stokn = C::TOK_ON_M ? __ldcg(tsp + (size_t)min(gb * C::KPB, p.KB - 1) * p.rows_cap) : 0.f;
-            // GEMM2, tokens on M: the routing weight of this thread's row, fetched before the K loop
-            const float wrow = (C::TOK_ON_M && !G1 && m < un.nvalid) ? __ldg(p.row_w + un.row0 + m) : 0.f;
             for (int grp = gb; grp < ge; ++grp) {
                 const int kb0 = grp * C::KPB;
                 const int nj = min(C::KPB, p.KB - kb0);
@@ -835,7 +834,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
 #pragma unroll
                     for (int a = 0; a < C::NACCUM; ++a) {
                         const int col0 = un.mt * p.unit_rows + a * p.gate_offset + c0;
-                        if (col0 < p.valid_rows) store_y_row<C::NC>(p.y + row * p.H + col0, acc[a], wrow);
+                        if (col0 < p.valid_rows) store_y_row<C::NC>(p.y + row * p.H + col0, acc[a]);
                     }
                 }
             } else if (G1) {
@@ -886,9 +885,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     const int c = c0 + i;
                     if (c < un.nvalid) {
                         const size_t row = (size_t)(un.row0 + c);
-                        const float w = __ldg(p.row_w + row);
-                        p.y[row * p.H + col0] = __float2half_rn(acc[0][i] * w);
-                        if (second) p.y[row * p.H + col0 + p.gate_offset] = __float2half_rn(acc[1][i] * w);
+                        p.y[row * p.H + col0] = __float2half_rn(acc[0][i]);
+                        if (second) p.y[row * p.H + col0 + p.gate_offset] = __float2half_rn(acc[1][i]);
                     }
                 }
             }

@@ -22,8 +22,10 @@ enum : int { ST_ERR = 0, ST_PAIRS = 1, ST_ROWS = 2, ST_TILES = 3, ST_ACTIVE = 4 
 
 struct PlanParams {
     int T, top_k, num_local, local_offset, token_tile;
-    const int32_t* topk_idx;   // [T, top_k]
-    const float* topk_w;       // [T, top_k]
+    const int32_t* topk_idx;   // [T, top_k]: ids of token t start at topk_idx + t * pair_stride
+    const float* topk_w;       // [T, top_k]: weights of token t start at topk_w + t * pair_stride
+    int pair_stride;           // in 4-byte words: top_k for dense arrays; the row pitch when both live inside packed
+                               // dispatch rows (expert-parallel slots read in place)
     int* status;               // [8]
     const int* slices;         // [ceil(T*top_k / SLICE_PAIRS)][num_local] per-slice histogram (input)
     int* counts;               // [num_local] (output: totals)
@@ -37,12 +39,13 @@ struct PlanParams {
 
 // Per-slice histogram of the local experts from an explicit topk_idx (the expert-parallel receive
 // side, where routing ran on another rank); the routing kernel fills the same table itself.
-__global__ void count_kernel(const int32_t* __restrict__ topk_idx, int n, int local_offset, int num_local,
-                             int* __restrict__ slices) {
+__global__ void count_kernel(const int32_t* __restrict__ topk_idx, int n, int top_k, int pair_stride, int local_offset,
+                             int num_local, int* __restrict__ slices) {
     pdl_wait();
     pdl_launch();
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        const int le = topk_idx[i] - local_offset;
+        const int t = i / top_k;
+        const int le = topk_idx[(size_t)t * pair_stride + (i - t * top_k)] - local_offset;
         if (le >= 0 && le < num_local) atomicAdd(slices + (size_t)(i / SLICE_PAIRS) * num_local + le, 1);
     }
 }
@@ -131,7 +134,9 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const PlanPara
     // this thread's pair: rank among the pairs of the same expert that precede it in the warp
     const int n = p.T * p.top_k;
     const int i = c * SLICE_PAIRS + tid;
-    const int le = i < n ? __ldg(p.topk_idx + i) - p.local_offset : -1;
+    const int tok = i / p.top_k;
+    const size_t src = (size_t)tok * p.pair_stride + (i - tok * p.top_k);      // where pair i lives in topk_idx / topk_w
+    const int le = i < n ? __ldg(p.topk_idx + src) - p.local_offset : -1;
     const bool local = le >= 0 && le < El;
     const unsigned same = __match_any_sync(FULL, local ? le : -1 - lane);
     const int rank = __popc(same & ((1u << lane) - 1u));
@@ -165,8 +170,8 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const PlanPara
         const int r = s_row0[le] + s_before[le] + s_wcnt[warp][le] + rank;
         if (r < p.rows_cap) {
             p.pair_row[i] = r;
-            p.row_token[r] = i / p.top_k;
-            p.row_w[r] = p.topk_w[i];
+            p.row_token[r] = tok;
+            p.row_w[r] = p.topk_w[src];
         } else {
             // only reachable with expert ids from the caller that repeat an expert inside one token's row
             atomicCAS(p.status + ST_ERR, 0, ERR_BAD_SCHEDULE);
@@ -176,10 +181,13 @@ __global__ void __launch_bounds__(PERMUTE_THREADS) permute_kernel(const PlanPara
 
 // Expert-sorted copy of the fp8 activations and of their scales: a_perm[row] = hidden[token],
 // a_scale_perm[kb][row] = hidden_scale[kb][token].  One warp per row, grid-stride.
+// Source forms: the operator's layouts (row pitch H, scales K-block major in hscale[kb][token]) or - hscale ==
+// nullptr - packed dispatch rows read in place (row pitch `src_pitch` bytes, the token's H/128 scales right
+// behind its H fp8 bytes).
 __global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__ hidden, const float* __restrict__ hscale,
                                                      const int32_t* __restrict__ row_token, const int* __restrict__ status,
                                                      uint8_t* __restrict__ a_perm, float* __restrict__ a_scale_perm,
-                                                     int T, int H, int rows_cap) {
+                                                     int T, int H, int rows_cap, int src_pitch) {
     pdl_wait();
     pdl_launch();
     const int rows = status[ST_ROWS];
@@ -190,15 +198,22 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__
         const int t = row_token[r];
         uint4* dst = reinterpret_cast<uint4*>(a_perm + (size_t)r * H);
         if (t < 0) continue;   // padding rows stay unwritten: their columns are never stored by the GEMMs
-        const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * H);
+        const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * src_pitch);
         for (int i = lane; i < H / 16; i += 32) dst[i] = __ldg(src + i);
-        for (int kb = lane; kb < KB; kb += 32) a_scale_perm[(size_t)kb * rows_cap + r] = __ldg(hscale + (size_t)kb * T + t);
+        if (hscale) {
+            for (int kb = lane; kb < KB; kb += 32) a_scale_perm[(size_t)kb * rows_cap + r] = __ldg(hscale + (size_t)kb * T + t);
+        } else {
+            const float* ss = reinterpret_cast<const float*>(hidden + (size_t)t * src_pitch + H);
+            for (int kb = lane; kb < KB; kb += 32) a_scale_perm[(size_t)kb * rows_cap + r] = __ldg(ss + kb);
+        }
     }
 }
 
 // y holds one fp16 row per (token, expert) pair: 11 significant bits, half the traffic of fp32 rows in the
 // GEMM2 epilogue and here (bf16 rows - 8 bits - were tried first: the extra rounding of up to eight rows pushed
 // 1 element in 6.4 million over the 1e-2 / 1e-2 tolerance; fp16's error is an eighth of that).
+// The rows are the experts' outputs WITHOUT the routing weight: the weight multiplies in fp32 here, so the routed
+// scaling factor enters the result exactly once (doubling it doubles every output bit for bit).
 // out[t, :] = sum over the token's local pairs (ascending expert order = the order they were
 // placed in topk rows is NOT sorted, so sort the <= 8 rows by row index, which is expert
 // order) of y[row, :]; fp32 accumulation, one rounding.  Tokens without a local pair get zeros.
@@ -230,6 +245,14 @@ __device__ __forceinline__ uint4 pack8_f16(const float* a) {
     for (int q = 0; q < 4; ++q) o2[q] = __floats2half2_rn(a[2 * q], a[2 * q + 1]);
     return pk;
 }
+__device__ __forceinline__ void fma8_f16(float* acc, const uint4& v, float w) {
+    const __half2* v2 = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const float2 f = __half22float2(v2[q]);
+        acc[2 * q] = fmaf(w, f.x, acc[2 * q]); acc[2 * q + 1] = fmaf(w, f.y, acc[2 * q + 1]);
+    }
+}
 __device__ __forceinline__ void add8_f16(float* acc, const uint4& v) {
     const __half2* v2 = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
@@ -241,17 +264,18 @@ __device__ __forceinline__ void add8_f16(float* acc, const uint4& v) {
 
 template <int OUT>
 __global__ void __launch_bounds__(256) combine_kernel(const __half* __restrict__ y, const int32_t* __restrict__ topk_idx,
-                                                      const int32_t* __restrict__ pair_row, void* __restrict__ out,
-                                                      int T, int H, int top_k, int local_offset, int num_local,
-                                                      const SlotOut slots) {
+                                                      const int32_t* __restrict__ pair_row, const float* __restrict__ row_w,
+                                                      void* __restrict__ out, int T, int H, int top_k, int pair_stride,
+                                                      int local_offset, int num_local, const SlotOut slots) {
     __shared__ int s_rows[8];
+    __shared__ float s_w[8];
     __shared__ int s_n;
     pdl_wait();
     pdl_launch();
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
         uint16_t* out_row = reinterpret_cast<uint16_t*>(out) + (size_t)t * H;      // 2-byte kinds
         if (OUT == OUT_F16 && slots.cap > 0) {
-            if (topk_idx[(size_t)t * top_k] < 0) continue;          // same for the whole CTA
+            if (topk_idx[(size_t)t * pair_stride] < 0) continue;    // same for the whole CTA
             const int r = t / slots.cap;
             out_row = static_cast<uint16_t*>(slots.back.p[r]) + ((size_t)slots.my_rank * slots.cap + (t - r * slots.cap)) * H;
         }
@@ -261,7 +285,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const __half* __restrict__
             const int lane = threadIdx.x;
             int r = 0x7FFFFFFF;
             if (lane < top_k) {
-                const int le = topk_idx[(size_t)t * top_k + lane] - local_offset;
+                const int le = topk_idx[(size_t)t * pair_stride + lane] - local_offset;
                 if (le >= 0 && le < num_local) r = pair_row[(size_t)t * top_k + lane];
             }
             int rank = 0;
@@ -270,14 +294,14 @@ __global__ void __launch_bounds__(256) combine_kernel(const __half* __restrict__
                 rank += (rj < r) || (rj == r && j < lane);
             }
             const unsigned have = __ballot_sync(0xFFFFFFFFu, r != 0x7FFFFFFF);
-            if (r != 0x7FFFFFFF) s_rows[rank] = r;
+            if (r != 0x7FFFFFFF) { s_rows[rank] = r; s_w[rank] = __ldg(row_w + r); }
             if (lane == 0) s_n = __popc(have);
         }
         __syncthreads();
         const int n = s_n;
         for (int h = threadIdx.x * 8; h < H; h += blockDim.x * 8) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int j = 0; j < n; ++j) add8_f16(acc, *reinterpret_cast<const uint4*>(y + (size_t)s_rows[j] * H + h));
+            for (int j = 0; j < n; ++j) fma8_f16(acc, *reinterpret_cast<const uint4*>(y + (size_t)s_rows[j] * H + h), s_w[j]);
             if (OUT == OUT_BF16) {
                 *reinterpret_cast<uint4*>(out_row + h) = pack8_bf16(acc);
             } else if (OUT == OUT_F16) {

@@ -201,17 +201,17 @@ class PeerExchange:
                     "b200moe_ep_unpack_slots")
         return x, sc, idx, w
 
-    def experts_to_peers(self, idx, w, hidden, hscale, weights, offset):
-        """The local experts over all wire slots; the last kernel stores every present slot's fp16 partial row straight
-        into its owner's back slot (b200moe_forward_routed_slots: no intermediate buffer, no return copy)."""
+    def experts_to_peers(self, weights, offset):
+        """The local experts over all wire slots, read in place (no unpack copy); the last kernel stores every
+        present slot's fp16 partial row straight into its owner's back slot (b200moe_forward_routed_slots)."""
         n = self.world * self.cap
         ws = self.layer.workspace(n)
-        self._keep2 = (idx, w, hidden, hscale)
-        ptrs = [t.data_ptr() for t in (idx, w, hidden, hscale, weights["gemm1_weights"], weights["gemm1_weights_scale"],
-                                       weights["gemm2_weights"], weights["gemm2_weights_scale"])]
-        self._check(self._lib.lib.b200moe_forward_routed_slots(self.layer._h, *ptrs, self.cap, self.world, self.rank,
-                                                               int(offset), self.peer_back, ws.data_ptr(), ws.numel(),
-                                                               self._stream()), "b200moe_forward_routed_slots")
+        ptrs = [weights[k].data_ptr() for k in ("gemm1_weights", "gemm1_weights_scale", "gemm2_weights",
+                                               "gemm2_weights_scale")]
+        self._check(self._lib.lib.b200moe_forward_routed_slots(self.layer._h, self.wire.data_ptr(), *ptrs, self.cap,
+                                                               self.world, self.rank, int(offset), self.peer_back,
+                                                               ws.data_ptr(), ws.numel(), self._stream()),
+                    "b200moe_forward_routed_slots")
 
     def give_back(self, part, idx_slots):
         self._check(self._lib.lib.b200moe_ep_return(self.layer._h, part.data_ptr(), idx_slots.data_ptr(), self.cap,
@@ -274,9 +274,7 @@ class ExpertParallelMoE:
             mark("push")
             px.barrier()
             mark("barrier1")
-            x_recv, sc_recv, idx_recv, w_recv = px.unpack()
-            mark("unpack")
-            px.experts_to_peers(idx_recv, w_recv, x_recv, sc_recv, be.w, be.offset)     # result rows go straight home
+            px.experts_to_peers(be.w, be.offset)      # reads the slots in place; result rows go straight home
             mark("experts")
             px.barrier()
             mark("barrier2")
@@ -308,10 +306,11 @@ class ExpertParallelMoE:
         return out
 
     def launches_per_step(self) -> int:
-        """Kernels of this library one step launches on one rank.  Peer-memory form: route, push, barrier, slot
-        unpack, count, permute, gather, GEMM1, GEMM2, combine (stores into the owners' slots), barrier, owner-side
-        sum; collective form: route, pack, unpack, count, permute, gather, GEMM1, GEMM2, combine, owner-side sum."""
-        return 12 if self.peer is not None else 10
+        """Kernels of this library one step launches on one rank.  Peer-memory form: route, push, barrier, count,
+        permute, gather (from the wire slots), GEMM1, GEMM2, combine (stores into the owners' slots), barrier,
+        owner-side sum; collective form: route, pack, unpack, count, permute, gather, GEMM1, GEMM2, combine,
+        owner-side sum."""
+        return 11 if self.peer is not None else 10
 
     def check_status(self):
         """Raises if a barrier of the peer-memory exchange gave up waiting for a peer since the last check (the

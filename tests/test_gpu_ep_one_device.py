@@ -71,6 +71,7 @@ def test_all_ranks_on_one_device_match_the_oracle(world):
     _check(emu.step_peer(toks, rsf), want, "peer-memory exchange, step 1")
     _check(emu.step_peer(toks, rsf), want, "peer-memory exchange, step 2 (slots reused, epochs grow)")
     _check(emu.step_alltoall(toks, rsf), want, "all-to-all form")
+    _check(emu.step_peer_long(toks, rsf), want, "peer-memory exchange through the stand-alone entry points")
     # a step in which rank 0 brings no token at all
     toks0 = [(toks[0][0][:0], toks[0][1], toks[0][2][:0], toks[0][3][:, :0].contiguous())] + toks[1:]
     outs = emu.step_peer(toks0, rsf)
