@@ -77,10 +77,10 @@ typedef struct b200moe_ws_layout {
     size_t act_lo;        /* uint8[rows_cap, I] e4m3 of the rounding residual              */
     size_t act_scale;     /* float[I/128, rows_cap]                                        */
     size_t y;             /* fp16[rows_cap, H] expert output per row (before the weight)   */
-    size_t sk_count;      /* int32[2][4*SMs] arrival counters of K-split units (GEMM1, GEMM2)*/
+    size_t sk_count;      /* int32[2][4*SMs+4] per GEMM: arrival counters of chunked units, chunk claim counter */
     size_t slices;        /* int32[ceil(T*top_k/1024)][E_local] histogram of the local experts per
                              slice of 1024 (token, expert) pairs, token-major                */
-    size_t sk_partial;    /* float[2*SMs][32768] fp32 partial accumulators of K-split units */
+    size_t sk_partial;    /* fp32 partial accumulators of the chunked units: slot (unit, chunk) */
     size_t trace;         /* int64[2][SMs][16] per-CTA time lines of GEMM1 and GEMM2: slot 0 =
                              %globaltimer at entry, slots 1..11 = SM clocks since entry at:
                              prologue done, first/last TMA issue, first/last MMA, first/last

@@ -126,6 +126,24 @@ int pick_token_tile(const b200moe_config& c, int T) {
     return 128;
 }
 
+// Partial-sum slots of the chunked units: (fewer than grid units) x (chunks per unit) x (floats per slot), the larger
+// of the two GEMMs (they run one after the other and share the area).
+template <int NTOK>
+size_t sk_partial_bytes_ntok(const b200moe_config& c, int grid) {
+    using C1 = GemmCfg<NTOK, true>; using C2 = GemmCfg<NTOK, false>;
+    const size_t a = (size_t)chunks_per_unit(c.hidden / 128, C1::KPB, C1::CHUNK_GROUPS) * C1::SLOT_FLOATS;
+    const size_t b = (size_t)chunks_per_unit(c.intermediate / 128, C2::KPB, C2::CHUNK_GROUPS) * C2::SLOT_FLOATS;
+    return (a > b ? a : b) * (size_t)grid * 4;
+}
+size_t sk_partial_bytes(const b200moe_config& c, int grid, int ntok) {
+    switch (ntok) {
+        case 16: return sk_partial_bytes_ntok<16>(c, grid);
+        case 32: return sk_partial_bytes_ntok<32>(c, grid);
+        case 64: return sk_partial_bytes_ntok<64>(c, grid);
+        default: return sk_partial_bytes_ntok<128>(c, grid);
+    }
+}
+
 int rows_capacity_for(const b200moe_config& c, int T) {
     const long long per_tok = c.top_k < c.num_local_experts ? c.top_k : c.num_local_experts;
     long long rows = (long long)T * per_tok + (long long)ROW_ALIGN * c.num_local_experts;
@@ -142,7 +160,7 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, A); return o; };
     L->status = take(8 * 4);
     L->counts = take((size_t)El * 4);
-    L->sk_count = take((size_t)2 * 4 * h->num_sms * 4);       // [GEMM1 | GEMM2][4 * grid]; zeroed with the head
+    L->sk_count = take((size_t)2 * (4 * h->num_sms + 4) * 4); // [GEMM1 | GEMM2][4 * grid + 4]; zeroed with the head
     L->slices = take((size_t)num_slices(c, T) * El * 4);      // zeroed with the head
     L->expert_row0 = take((size_t)(El + 1) * 4);
     L->tile_prefix = take((size_t)(El + 1) * 4);
@@ -157,7 +175,7 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     L->act_lo = take(rows * c.intermediate);
     L->act_scale = take((size_t)(c.intermediate / 128) * rows * 4);
     L->y = take(rows * c.hidden * 2);
-    L->sk_partial = take((size_t)2 * h->num_sms * SK_SLOT_FLOATS_MAX * 4);
+    L->sk_partial = take(sk_partial_bytes(c, h->num_sms, (int)pick_token_tile(c, T)));
     L->trace = take((size_t)2 * h->num_sms * TRACE_SLOTS * 8 + 2 * 8 * KLOG_N * 8);   // [GEMM1 | GEMM2][CTA][slot], then K-block logs
     L->rows_cap = rows;
     L->token_tile = (size_t)pick_token_tile(c, T);
@@ -397,7 +415,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g2.w_scale = static_cast<const float*>(s2); g2.b_scale = act_scale; g2.rows_cap = rows_cap;
     g2.row_w = row_w; g2.y = y; g2.H = H; g2.I = I;
     g2.evict_first_weights = evf && ntok < 128;
-    g2.sk_count = reinterpret_cast<int*>(ws + L.sk_count) + 4 * h->num_sms;
+    g2.sk_count = reinterpret_cast<int*>(ws + L.sk_count) + 4 * h->num_sms + 4;
     g2.sk_partial = g1.sk_partial;
     g2.ablate = (h->ablate >> 8) & 0xFF;
     g2.trace = g1.trace + (size_t)h->num_sms * TRACE_SLOTS;

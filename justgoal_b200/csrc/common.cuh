@@ -16,7 +16,9 @@ enum : int {
     ERR_WAIT_TMEM_EMPTY = 3,   // MMA warp gave up waiting for a free accumulator buffer
     ERR_WAIT_TMEM_FULL = 4,    // promotion warps gave up waiting for MMA results
     ERR_BAD_SCHEDULE = 5,      // unit decoded outside the expert tables
-    ERR_WAIT_GROUP = 6,        // epilogue warps of one column group gave up waiting for each other
+    ERR_WAIT_GROUP = 6,        // epilogue warps of one column group gave up waiting for each other (or for the work queue)
+    // 7 = a rank gave up waiting for a peer's barrier flag (ep_p2p.cuh)
+    ERR_WAIT_CHUNKS = 8,       // the finisher of a chunked unit gave up waiting for the other chunks' partial sums
 };
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // every device-side wait gives up after 2 s

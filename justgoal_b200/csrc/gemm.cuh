@@ -16,13 +16,20 @@
 // unlike them the SwiGLU output keeps a second e4m3 term, because a single e4m3 per element
 // does not meet an absolute/relative tolerance of 1e-2 against the unquantised definition.
 //
-// Schedule: K is cut into GROUPS of KPB 128-K blocks (one TMEM hand-off per group).  The
-// kernel is persistent; the flat list of (unit, group) pairs is cut into gridDim.x equal
-// contiguous ranges ("stream-K"), so every SM streams weights for the whole kernel.  A unit
-// whose groups fall into several CTAs is finished by whichever of them arrives last: each
-// writes its fp32 partial to its own slot, bumps a counter, and the last one adds the slots in
-// CTA order (a fixed order: results are bit-identical from run to run) and runs the epilogue.
-// Nobody waits for another CTA.
+// Schedule: K is cut into GROUPS of KPB 128-K blocks (one TMEM hand-off per group).  The kernel is
+// persistent.  Units are numbered so that the token tiles of one (expert, row tiles) are adjacent.  Every CTA
+// first runs floor(U / grid) WHOLE units, round-robin (CTAs that run at the same time work on adjacent units, so
+// a weight tile shared by several token tiles comes from HBM once).  The remaining U mod grid units are cut
+// along K into CHUNKS of a few K blocks, and the CTAs CLAIM those chunks one at a time from a counter in global
+// memory: SMs do not stream at the same rate under full load, and a CTA that finishes early simply takes more
+// chunks (with equal static shares the finish times of the CTAs spread by 7-10 % of the kernel).  A chunked
+// unit is finished by whichever CTA delivers its last chunk: every chunk's fp32 partial goes to its own slot,
+// unit is finished by the CTA that runs its LAST chunk: every other chunk stores its fp32 partial to its own slot
+// and counts itself in with a release; the finisher waits (bounded) for that count, adds the slots in CHUNK order
+// (a fixed order: results are bit-identical from run to run) and runs the epilogue.  Chunks are claimed in order, so
+// the finisher only ever waits for chunks that were claimed before its own - no cycle of waiting CTAs can form.
+// Inside a CTA the producer claims the work and hands it to the MMA and promotion warps through a small queue
+// in shared memory.
 //
 // Warp roles: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) + TMEM owner,
 // warps 2-3 idle (they complete the first warpgroup so register re-allocation is legal),
@@ -56,8 +63,9 @@ struct GemmParams {
     const float* row_w; __half* y; int H;                         // GEMM2 output: y[row, h] = O[row, h] as fp16 (the routing
                                                                   // weight is applied by the combine, in fp32)
     int evict_first_weights;
-    int* sk_count;        // [4 * gridDim.x] arrival counters of split units (zero at launch)
-    float* sk_partial;    // [2 * gridDim.x] slots of SLOT_FLOATS floats
+    int* sk_count;        // [4 * gridDim.x + 4] zero at launch: [4 * ut] promotion warps of chunked unit ut that have stored
+                          // their partial sums, [4 * gridDim.x] the chunk claim counter
+    float* sk_partial;    // [gridDim.x * chunks per unit] slots of SLOT_FLOATS floats: slot (ut, chunk)
     long long* klog;      // [4][KLOG_N]: CTA 0's clock at its first KLOG_N K blocks: TMA issue, data seen by the
                           // MMA warp, group seen by the promotion warps, group folded (hand-back)
     long long* trace;     // [gridDim.x][TRACE_SLOTS]: slot 0 = %globaltimer at entry, others = SM clocks since entry
@@ -125,9 +133,20 @@ struct GemmCfg {
     // stage has landed and release the stage at once, instead of holding it until the group is folded
     static constexpr bool EARLY_SCALES = KPB * NC <= 32 && NPW < 16;
     static constexpr int SLOT_FLOATS = NACCUM * NC * NPT;  // = NACCUM * 128 * NTOK
+    // K blocks per claimed chunk of a split unit: ~128 KB of weights for narrow tiles (a few microseconds of
+    // streaming); wide tiles carry 64-128 KB of partial sums per chunk, so their units are cut into few chunks
+    static constexpr int CHUNK_BLOCKS = NTOK <= 64 ? 8 : 16;
+    static constexpr int CHUNK_GROUPS = (CHUNK_BLOCKS / KPB) < 1 ? 1 : (CHUNK_BLOCKS / KPB);
+    // GEMM1 with narrow tiles has few, long units (decode: 256 units of 3.7 MB for 148 CTAs): there the units left
+    // over after the whole rounds are cut into EQUAL contiguous ranges, one per CTA, processed first (claimed
+    // chunks measured 30 % slower there: every CTA finishes units it has to collect six partial sums for, late in
+    // the kernel).  Everywhere else the left-over units are cut into chunks that the CTAs claim as they go.
+    static constexpr bool STATIC_TAIL = G1 && NTOK <= 32;
+    static constexpr int WQ = 4;                           // depth of the in-CTA work queue
+    static constexpr int BAR_BYTES = 320;                  // mbarriers + TMEM address word
     static constexpr int TABLE_INTS = 3 * (MAX_LOCAL + 1);
     static constexpr int RED_BYTES = NPW * NC * 4;
-    static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * STAGE_BYTES + 256 /*barriers*/ +
+    static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * STAGE_BYTES + BAR_BYTES + WQ * 32 /*work queue*/ +
                                       TABLE_INTS * 4 + RED_BYTES + 32;
     static_assert(NTOK % 16 == 0 && NTOK >= 16 && NTOK <= 128, "token tile");
     static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "tmem");
@@ -136,7 +155,6 @@ struct GemmCfg {
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 };
 
-constexpr int SK_SLOT_FLOATS_MAX = 2 * 128 * 128;   // largest SLOT_FLOATS (GEMM1, 128 tokens)
 
 // Per-CTA time line (SM clock cycles since kernel entry) written by whichever thread reaches the point.
 enum : int { TR_ENTRY = 0, TR_PROLOGUE = 1, TR_TMA_FIRST = 2, TR_TMA_LAST = 3, TR_MMA_FIRST = 4, TR_MMA_LAST = 5,
@@ -165,41 +183,28 @@ __device__ __forceinline__ bool decode_unit(int u, int n_mtiles, int num_local, 
     return o.mt < n_mtiles && o.nvalid > 0;
 }
 
-// First flat (unit, group) index of CTA c, and the CTA that owns flat index x.
-__device__ __forceinline__ long long sk_start(long long c, long long total, long long grid) { return c * total / grid; }
-__device__ __forceinline__ int sk_owner(long long x, long long total, long long grid) {
-    long long c = x * grid / total;
-    while (c + 1 < grid && sk_start(c + 1, total, grid) <= x) ++c;
-    while (c > 0 && sk_start(c, total, grid) > x) --c;
+// One piece of work: unit u, K groups [gb, ge).  kind WK_WHOLE: the whole unit.  WK_PART: a piece of split unit ut
+// that does not end the unit - its partial sum goes to slot `slot`.  WK_FINISH: the piece that ends split unit ut -
+// it waits for `nwait` other pieces, adds the slots slot .. slot + nwait - 1 in that order and runs the epilogue.
+// u < 0 ends the list.
+enum : int { WK_WHOLE = 0, WK_PART = 1, WK_FINISH = 2 };
+struct WorkItem { int u, gb, ge, kind, ut, slot, nwait; };
+
+// CTA that owns flat index x when `total` indices are cut into `parts` equal contiguous ranges (part c starts at
+// c * total / parts)
+__device__ __forceinline__ long long range_start(long long c, long long total, long long parts) { return c * total / parts; }
+__device__ __forceinline__ int range_owner(long long x, long long total, long long parts) {
+    long long c = x * parts / total;
+    while (c + 1 < parts && range_start(c + 1, total, parts) <= x) ++c;
+    while (c > 0 && range_start(c, total, parts) > x) --c;
     return (int)c;
 }
 
-// Per-CTA work list: one contiguous range of the K-split units, then q whole units.
-struct SkSched { int NG, q, U0; long long total, grid, t_lo, t_hi; };
-struct SkSeg { int u, gb, ge; bool tail_first; };
-struct SkIter {
-    int i; long long g;
-    __device__ __forceinline__ void reset(const SkSched& s) { i = 0; g = s.t_lo; }
-    // The K-split range comes FIRST: its partial sums are published and added up while every CTA
-    // still has whole units to stream, so the fix-up latency is hidden behind useful traffic.
-    __device__ __forceinline__ bool next(const SkSched& s, SkSeg& o) {
-        if (g < s.t_hi) {
-            const int ut = (int)(g / s.NG);
-            o.gb = (int)(g - (long long)ut * s.NG);
-            o.ge = (int)min((long long)s.NG, o.gb + (s.t_hi - g));
-            o.u = s.U0 + ut;
-            o.tail_first = (g == s.t_lo);
-            g += o.ge - o.gb;
-            return true;
-        }
-        if (i < s.q) {
-            o.u = i * (int)gridDim.x + (int)blockIdx.x; o.gb = 0; o.ge = s.NG; o.tail_first = false;
-            ++i;
-            return true;
-        }
-        return false;
-    }
-};
+// Chunks per chunked unit
+__host__ __device__ inline int chunks_per_unit(int KB, int kpb, int chunk_groups) {
+    const int NG = (KB + kpb - 1) / kpb;
+    return (NG + chunk_groups - 1) / chunk_groups;
+}
 
 __device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
@@ -258,9 +263,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tail = smem + C::STAGES * C::STAGE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tail);     // full[S], empty[S], tfull[NTB], tempty[NTB], red[2]
-    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tail + 240);
-    int* s_tiles = reinterpret_cast<int*>(tail + 256);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail);     // full[S], empty[S], tfull[NTB], tempty[NTB], red[4], all, wq_full[WQ], wq_empty[WQ]
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tail + C::BAR_BYTES - 8);
+    int* s_wq = reinterpret_cast<int*>(tail + C::BAR_BYTES);          // [WQ][8] work items (WorkItem + padding)
+    int* s_tiles = s_wq + C::WQ * 8;
     int* s_row0 = s_tiles + (MAX_LOCAL + 1);
     int* s_cnt = s_row0 + (MAX_LOCAL + 1);
     uint32_t* s_red = reinterpret_cast<uint32_t*>(s_cnt + (MAX_LOCAL + 1));
@@ -288,13 +294,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     const uint32_t bar_tempty = bar_tfull + 8 * C::NTB;
     const uint32_t bar_red = bar_tempty + 8 * C::NTB;    // one per column group: its 4 warps meet here (bounded)
     const uint32_t bar_all = bar_red + 8 * 4;             // all promotion warps meet here (tokens-on-M epilogue)
-    static_assert(8 * (2 * C::STAGES + 2 * C::NTB + 5) <= 240, "barrier area");
+    const uint32_t bar_wqfull = bar_all + 8;              // work queue: the producer has published item n
+    const uint32_t bar_wqempty = bar_wqfull + 8 * C::WQ;  // ... and the MMA warp and every promotion warp have read it
+    static_assert(8 * (2 * C::STAGES + 2 * C::NTB + 5 + 2 * C::WQ) <= C::BAR_BYTES - 8, "barrier area");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, C::EMPTY_COUNT); }
         for (int b = 0; b < C::NTB; ++b) { mbar_init(bar_tfull + 8 * b, 1); mbar_init(bar_tempty + 8 * b, C::NPW); }
         for (int g = 0; g < 4; ++g) mbar_init(bar_red + 8 * g, 4);
         mbar_init(bar_all, C::NPW);
+        for (int w = 0; w < C::WQ; ++w) { mbar_init(bar_wqfull + 8 * w, 1); mbar_init(bar_wqempty + 8 * w, 1 + C::NPW); }
         mbar_fence_init();
         tma_prefetch_desc(&tm_w); tma_prefetch_desc(&tm_b0);
         if (!G1) tma_prefetch_desc(&tm_b1);
@@ -316,25 +325,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     const uint32_t smem_base = smem_u32(smem);
     if (threadIdx.x == 0) stamp(TR_PROLOGUE);
 
-    // Schedule.  Units are numbered so that the token tiles of one (expert, row tile) are adjacent.
-    // The first q*gridDim.x units run as whole units, round-robin (CTAs that run at the same time
-    // work on adjacent units, so a weight tile shared by several token tiles comes from HBM once and
-    // from L2 afterwards).  The remaining units (fewer than gridDim.x) are cut along K: their
-    // (unit, group) pairs are split into equal contiguous ranges, one per CTA.
+    // Schedule (see the head of this file): q whole units per CTA, then chunks of the remaining units claimed
+    // from a global counter.
     const int NG = (p.KB + C::KPB - 1) / C::KPB;
     const int total_units = s_tiles[p.num_local] * p.n_mtiles;
-    SkSched sc;
-    sc.NG = NG;
-    sc.q = total_units / (int)gridDim.x;
-    sc.U0 = sc.q * (int)gridDim.x;
-    sc.total = (long long)(total_units - sc.U0) * NG;
-    // with fewer pairs than CTAs only the first `total` CTAs take part, so that every participating
-    // CTA owns at least one pair (the split-unit bookkeeping counts on that)
-    sc.grid = sc.total < (long long)gridDim.x ? (sc.total > 0 ? sc.total : 1) : (long long)gridDim.x;
-    const bool has_tail = (long long)blockIdx.x < sc.grid && sc.total > 0;
-    sc.t_lo = has_tail ? sk_start(blockIdx.x, sc.total, sc.grid) : 0;
-    sc.t_hi = has_tail ? sk_start(blockIdx.x + 1, sc.total, sc.grid) : 0;
-    const long long total = sc.total, grid = sc.grid;
+    const int sched_q = total_units / (int)gridDim.x;              // whole units per CTA
+    const int sched_U0 = sched_q * (int)gridDim.x;                 // first chunked unit
+    const int CPU_ = (NG + C::CHUNK_GROUPS - 1) / C::CHUNK_GROUPS; // chunks per chunked unit
+    const int total_chunks = (total_units - sched_U0) * CPU_;
+    int* const claim = p.sk_count + 4 * (int)gridDim.x;
+
+    // Consumer side of the work queue: item n sits in slot n % WQ.  WARP: every lane of the calling warp waits and
+    // reads, lane 0 then tells the producer that the warp has its copy; otherwise the caller is a single thread.
+    // false = list ended or a wait gave up.
+    auto wq_fetch = [&](int n, WorkItem& w, bool& ok, bool whole_warp) -> bool {
+        const int slot = n % C::WQ;
+        if (!mbar_wait(bar_wqfull + 8 * slot, (uint32_t)(n / C::WQ) & 1u, p.status, ERR_WAIT_GROUP)) { ok = false; return false; }
+        const volatile int* q = s_wq + slot * 8;
+        w.u = q[0]; w.gb = q[1]; w.ge = q[2]; w.kind = q[3]; w.ut = q[4]; w.slot = q[5]; w.nwait = q[6];
+        if (whole_warp) __syncwarp();
+        if (!whole_warp || lane == 0) mbar_arrive(bar_wqempty + 8 * slot);
+        return w.u >= 0;
+    };
 
     if (warp < 4) {
     // ================================================================ control warpgroup
@@ -348,13 +360,75 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             int stage = 0; uint32_t phase = 0;
             bool ok = true, issued = false;
             int nk = 0;
-            SkIter it; it.reset(sc);
-            SkSeg sg;
-            while (ok && it.next(sc, sg)) {
-                const int u = sg.u, gb = sg.gb, ge = sg.ge;
+            // the producer decides what this CTA does next and publishes it to the other roles
+            int n_item = 0, n_whole = 0;
+            auto publish = [&](const WorkItem& w) -> bool {
+                const int slot = n_item % C::WQ;
+                if (!mbar_wait(bar_wqempty + 8 * slot, ((uint32_t)(n_item / C::WQ) & 1u) ^ 1u, p.status, ERR_WAIT_GROUP)) return false;
+                volatile int* q = s_wq + slot * 8;
+                q[0] = w.u; q[1] = w.gb; q[2] = w.ge; q[3] = w.kind; q[4] = w.ut; q[5] = w.slot; q[6] = w.nwait;
+                mbar_arrive(bar_wqfull + 8 * slot);          // release: the item is visible to whoever sees the phase flip
+                ++n_item;
+                return true;
+            };
+            // static tail: this CTA's range [t_lo, t_hi) of the flat (left-over unit, K group) space, as per-unit pieces;
+            // pieces that do not end their unit come first, then the one that does (it waits for pieces other CTAs
+            // run first, so no chain of waiting CTAs can form), then whole units
+            const int tail_units = total_units - sched_U0;
+            const long long flat = (long long)tail_units * NG;
+            const long long parts = flat < (long long)gridDim.x ? (flat > 0 ? flat : 1) : (long long)gridDim.x;
+            const bool has_tail = C::STATIC_TAIL && flat > 0 && (long long)blockIdx.x < parts;
+            const long long t_lo = has_tail ? range_start(blockIdx.x, flat, parts) : 0;
+            const long long t_hi = has_tail ? range_start(blockIdx.x + 1, flat, parts) : 0;
+            int st_pass = has_tail ? 0 : 3, st_ut = (int)(t_lo / NG);
+            while (ok) {
+                WorkItem wi;
+                wi.kind = WK_WHOLE; wi.ut = -1; wi.slot = 0; wi.nwait = 0;
+                bool have = false;
+                while (st_pass < 3 && !have) {
+                    const int ut_last = (int)((t_hi - 1) / NG);
+                    while (st_ut <= ut_last && !have) {
+                        const int ut = st_ut++;
+                        const long long u_lo = (long long)ut * NG;
+                        const int gb = (int)(max(t_lo, u_lo) - u_lo), ge = (int)(min(t_hi, u_lo + NG) - u_lo);
+                        const int kind = (gb == 0 && ge == NG) ? WK_WHOLE : (ge == NG ? WK_FINISH : WK_PART);
+                        const int want = st_pass == 0 ? WK_PART : (st_pass == 1 ? WK_FINISH : WK_WHOLE);
+                        if (kind != want) continue;
+                        wi.u = sched_U0 + ut; wi.gb = gb; wi.ge = ge; wi.kind = kind; wi.ut = ut;
+                        if (kind == WK_PART) {
+                            wi.slot = (int)blockIdx.x;              // a CTA stores at most one partial: its own slot
+                        } else if (kind == WK_FINISH) {
+                            wi.slot = range_owner(u_lo, flat, parts);          // CTA of the unit's first piece
+                            wi.nwait = (int)blockIdx.x - wi.slot;
+                            if (wi.nwait == 0) wi.kind = WK_WHOLE;             // cannot happen (gb > 0), kept for safety
+                        }
+                        have = true;
+                    }
+                    if (!have) { ++st_pass; st_ut = (int)(t_lo / NG); }
+                }
+                if (have) {
+                } else if (n_whole < sched_q) {
+                    wi.u = n_whole * (int)gridDim.x + (int)blockIdx.x; wi.gb = 0; wi.ge = NG;
+                    ++n_whole;
+                } else {
+                    const int c = (!C::STATIC_TAIL && total_chunks > 0) ? atomicAdd(claim, 1) : total_chunks;
+                    if (c >= total_chunks) { wi.u = -1; wi.gb = wi.ge = 0; publish(wi); break; }
+                    wi.ut = c / CPU_;
+                    const int ci = c - wi.ut * CPU_;
+                    wi.u = sched_U0 + wi.ut;
+                    wi.gb = ci * C::CHUNK_GROUPS; wi.ge = min(NG, wi.gb + C::CHUNK_GROUPS);
+                    if (CPU_ > 1) {
+                        // chunks are claimed in order: the one that ends the unit is claimed last and finishes it
+                        wi.kind = ci + 1 < CPU_ ? WK_PART : WK_FINISH;
+                        wi.slot = wi.kind == WK_PART ? wi.ut * CPU_ + ci : wi.ut * CPU_;
+                        wi.nwait = CPU_ - 1;
+                    }
+                }
+                if (!publish(wi)) { ok = false; break; }
+                const int u = wi.u, gb = wi.gb, ge = wi.ge;
                 Unit un;
                 if (!decode_unit(u, p.n_mtiles, p.num_local, NTOK, s_tiles, s_row0, s_cnt, un)) {
-                    atomicCAS(p.status, 0, ERR_BAD_SCHEDULE); break;
+                    atomicCAS(p.status, 0, ERR_BAD_SCHEDULE); ok = false; break;
                 }
                 const int wrow = un.e * p.rows_per_expert + un.mt * p.unit_rows;
                 const int kb_end = min(p.KB, ge * C::KPB);
@@ -383,7 +457,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             }
             stamp(TR_TMA_LAST);
             if (!ok) {
-                // give copies that are still in flight time to land before the CTA's shared memory goes away
+                // gave up: end the list for the other roles (if the queue still moves), then give copies that are
+                // still in flight time to land before the CTA's shared memory goes away
+                WorkItem end_; end_.u = -1; end_.gb = end_.ge = 0; end_.kind = WK_WHOLE; end_.ut = -1; end_.slot = end_.nwait = 0;
+                publish(end_);
                 for (int i = 0; i < 64; ++i) __nanosleep(10000);
             }
         }
@@ -396,10 +473,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             int ab = 0; uint32_t aphase = 0;
             bool ok = true, seen = false;
             int nk = 0;
-            SkIter it; it.reset(sc);
-            SkSeg sg;
-            while (ok && it.next(sc, sg)) {
-                const int gb = sg.gb, ge = sg.ge;
+            int n_item = 0;
+            WorkItem wi;
+            while (ok && wq_fetch(n_item++, wi, ok, false)) {
+                const int gb = wi.gb, ge = wi.ge;
                 if (kAblate & 8) {      // timing experiment: consume stages directly, no MMA, no TMEM hand-off
                     const int kb_end = min(p.KB, ge * C::KPB);
                     for (int kb = gb * C::KPB; kb < kb_end && ok; ++kb) {
@@ -518,11 +595,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             return r;
         };
 
-        SkIter it; it.reset(sc);
-        SkSeg sg;
-        while (ok && !(kAblate & 8) && it.next(sc, sg)) {
-            const int u = sg.u, gb = sg.gb, ge = sg.ge;
-            const bool first_seg = sg.tail_first;
+        int n_item = 0;
+        WorkItem wi;
+        while (ok && wq_fetch(n_item++, wi, ok, true)) {
+            if (kAblate & 8) continue;          // timing experiment: the MMA warp consumes the stages alone
+            const int u = wi.u, gb = wi.gb, ge = wi.ge;
             Unit un;
             if (!decode_unit(u, p.n_mtiles, p.num_local, NTOK, s_tiles, s_row0, s_cnt, un)) break;
 #pragma unroll
@@ -717,50 +794,55 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             if (!ok) break;
             if (ptid == 0) stamp(TR_PROMO_LAST);
 
-            if (!(gb == 0 && ge == NG)) {
-                // ---- split unit: publish the partial, the last CTA to arrive adds them up in CTA order
-                const long long u0 = (long long)(u - sc.U0) * NG;      // tail-relative flat index of the unit's first pair
-                const int c_first = sk_owner(u0, total, grid), c_last = sk_owner(u0 + NG - 1, total, grid);
-                float* slot = p.sk_partial + (size_t)(blockIdx.x * 2 + (first_seg ? 0 : 1)) * SK_SLOT_FLOATS_MAX;
+            if (wi.kind != WK_WHOLE) {
+                // ---- piece of a split unit.  The unit is finished by the CTA that runs the piece that ends it.  Every
+                // other piece only stores its partial sums and counts its warps in with a release - no meeting of
+                // the warps, no answer to wait for.
+                int* const arrived = p.sk_count + wi.ut * 4;
+                if (wi.kind == WK_PART) {
+                    float* slot = p.sk_partial + (size_t)wi.slot * C::SLOT_FLOATS;
 #pragma unroll
-                for (int a = 0; a < C::NACCUM; ++a)
+                    for (int a = 0; a < C::NACCUM; ++a)
 #pragma unroll
-                    for (int i = 0; i < C::NC; ++i) __stcg(slot + (size_t)(a * C::NC + i) * C::NPT + ptid, acc[a][i]);
-                __threadfence();
-                // Who is last is decided per column group where the epilogue works per group (weights on M),
-                // but ONCE PER CTA with tokens on M: that epilogue reduces across the column groups (all
-                // promotion warps meet), so all of them must agree on which CTA runs it.
-                auto meet = [&]() -> bool { return C::TOK_ON_M ? all_sync() : group_sync(); };
-                const int cnt_id = C::TOK_ON_M ? 0 : grp_id;
-                if (!meet()) { ok = false; break; }
-                if (quarter == 0 && lane == 0 && (!C::TOK_ON_M || grp_id == 0)) {
-                    s_flag[cnt_id] = atomicAdd(p.sk_count + c_first * 4 + cnt_id, 1);
+                        for (int i = 0; i < C::NC; ++i) __stcg(slot + (size_t)(a * C::NC + i) * C::NPT + ptid, acc[a][i]);
+                    __syncwarp();        // orders the lanes' stores before lane 0's release below
+                    if (lane == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(arrived) : "memory");
+                    if (ptid == 0) stamp(TR_PARTIAL);
+                    continue;
                 }
-                if (!meet()) { ok = false; break; }
-                const bool last = s_flag[cnt_id] == (c_last - c_first);
-                if (!meet()) { ok = false; break; }                // s_flag may be rewritten by the next split unit
-                if (ptid == 0) stamp(TR_PARTIAL);
-                if (!last) continue;
-                __threadfence();
-#pragma unroll
-                for (int a = 0; a < C::NACCUM; ++a)
-#pragma unroll
-                    for (int i = 0; i < C::NC; ++i) acc[a][i] = 0.f;
-                auto slot_of = [&](int c) -> const float* {
-                    const bool c_first_seg = (int)(sk_start(c, total, grid) / NG) == u - sc.U0;
-                    return p.sk_partial + (size_t)(c * 2 + (c_first_seg ? 0 : 1)) * SK_SLOT_FLOATS_MAX + ptid;
-                };
+                // the piece that ends the unit: wait (bounded) until the warps of all other pieces have counted in, then
+                // add their partial sums in K order on top of this piece's own - a fixed order, whoever was quick or slow
+                const int n_other = wi.nwait;
+                const float* const slots = p.sk_partial + (size_t)wi.slot * C::SLOT_FLOATS;
+                {
+                    const int want = n_other * C::NPW;
+                    bool here = true;
+                    if (lane == 0) {
+                        const unsigned long long t0 = globaltimer_ns();
+                        for (uint32_t it = 1;; ++it) {
+                            int v;
+                            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(arrived) : "memory");
+                            if (v >= want) break;
+                            if ((it & 0xFFu) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                                atomicCAS(p.status, 0, ERR_WAIT_CHUNKS); here = false; break;
+                            }
+                        }
+                    }
+                    here = __shfl_sync(0xFFFFFFFFu, here, 0);
+                    if (!here) { ok = false; break; }
+                }
+                auto slot_of = [&](int c) -> const float* { return slots + (size_t)c * C::SLOT_FLOATS + ptid; };
                 if constexpr (C::NACCUM * C::NC <= 32) {
-                    // narrow tiles: the next CTA's slot is in flight while this one is added (same fixed order)
+                    // narrow tiles: the next chunk's slot is in flight while this one is added (same fixed order)
                     float nxt[C::NACCUM * C::NC];
-                    const float* src = slot_of(c_first);
+                    const float* src = slot_of(0);
 #pragma unroll
                     for (int k = 0; k < C::NACCUM * C::NC; ++k) nxt[k] = __ldcg(src + (size_t)k * C::NPT);
-                    for (int c = c_first; c <= c_last; ++c) {
+                    for (int c = 0; c < n_other; ++c) {
                         float cur[C::NACCUM * C::NC];
 #pragma unroll
                         for (int k = 0; k < C::NACCUM * C::NC; ++k) cur[k] = nxt[k];
-                        if (c < c_last) {
+                        if (c + 1 < n_other) {
                             src = slot_of(c + 1);
 #pragma unroll
                             for (int k = 0; k < C::NACCUM * C::NC; ++k) nxt[k] = __ldcg(src + (size_t)k * C::NPT);
@@ -771,7 +853,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                             for (int i = 0; i < C::NC; ++i) acc[a][i] += cur[a * C::NC + i];
                     }
                 } else {
-                    for (int c = c_first; c <= c_last; ++c) {
+                    for (int c = 0; c < n_other; ++c) {
                         const float* src = slot_of(c);
 #pragma unroll
                         for (int a = 0; a < C::NACCUM; ++a)
