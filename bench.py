@@ -563,7 +563,7 @@ def run_expert_parallel(args, name, spec, rank, world, local, K, W):
     for k in ("e2e", "gpu_launches", "clocks", "parity", "roofline", "layer", "phase_ms_rank0", "phase_ms_max_over_ranks",
               "phase_ms_min_over_ranks"):
         line[k] = rec[k]
-    if args.workload is None and world == 8:
+    if args.workload is None and (world == 8 or os.environ.get("B200MOE_BENCH_QWEN3")):     # configs[4] is an 8-GPU configuration
         torch.cuda.empty_cache()
         q = measure_expert_parallel("qwen3", workload_spec("qwen3", world), rank, world, local, K, W)
         line["workloads"] = {"qwen3": q}

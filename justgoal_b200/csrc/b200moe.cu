@@ -303,6 +303,28 @@ cudaError_t launch_route(int vpt, const RouteParams& rp, cudaStream_t st) {
     return cudaGetLastError();
 }
 
+template <int MODE>
+cudaError_t launch_front_route_mode(int vpt, int grid, const FrontParams& fp, const RouteParams& rp, cudaStream_t st) {
+    switch (vpt) {
+        case 1: return launch_k(PDL_PERMUTE, front_route_kernel<1, MODE>, dim3(grid), dim3(FRONT_THREADS), 0, st, fp, rp);
+        case 2: return launch_k(PDL_PERMUTE, front_route_kernel<2, MODE>, dim3(grid), dim3(FRONT_THREADS), 0, st, fp, rp);
+        case 4: return launch_k(PDL_PERMUTE, front_route_kernel<4, MODE>, dim3(grid), dim3(FRONT_THREADS), 0, st, fp, rp);
+        case 8: return launch_k(PDL_PERMUTE, front_route_kernel<8, MODE>, dim3(grid), dim3(FRONT_THREADS), 0, st, fp, rp);
+        default: return launch_k(PDL_PERMUTE, front_route_kernel<16, MODE>, dim3(grid), dim3(FRONT_THREADS), 0, st, fp, rp);
+    }
+}
+cudaError_t launch_front_route(const b200moe_config& c, int grid, const FrontParams& fp, const RouteParams& rp, cudaStream_t st) {
+    const int vpt = c.num_experts / 32;
+    switch (c.routing_mode) {
+        case B200MOE_ROUTING_DEEPSEEK: return launch_front_route_mode<RM_DEEPSEEK>(vpt, grid, fp, rp, st);
+        case B200MOE_ROUTING_RENORM_NAIVE: return launch_front_route_mode<RM_RENORM_NAIVE>(vpt, grid, fp, rp, st);
+        case B200MOE_ROUTING_DEFAULT: return launch_front_route_mode<RM_DEFAULT>(vpt, grid, fp, rp, st);
+        case B200MOE_ROUTING_RENORMALIZE: return launch_front_route_mode<RM_RENORMALIZE>(vpt, grid, fp, rp, st);
+        case B200MOE_ROUTING_LLAMA4: return launch_front_route_mode<RM_LLAMA4>(vpt, grid, fp, rp, st);
+        default: return launch_front_route_mode<RM_TOPK>(vpt, grid, fp, rp, st);
+    }
+}
+
 cudaError_t do_route(const b200moe_config& c, const RouteParams& rp, cudaStream_t st) {
     const int vpt = c.num_experts / 32;
     switch (c.routing_mode) {
@@ -328,7 +350,8 @@ inline cudaError_t prof_mark(b200moe_ctx* h, int point, cudaStream_t st) {
 int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, const void* hidden,
                 const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2, int T,
                 int local_offset, void* out, int out_kind, uint8_t* ws, const b200moe_ws_layout& L, cudaStream_t st,
-                bool fused_front = false, const SlotOut* slot_out = nullptr, int wire_pitch = 0) {
+                bool fused_front = false, const SlotOut* slot_out = nullptr, int wire_pitch = 0,
+                const RouteParams* route_in_front = nullptr) {
     // wire_pitch > 0: the tokens are packed dispatch rows read in place - `hidden` points at the first row,
     // topk_idx / topk_w at the ids / weights inside it, rows are wire_pitch bytes apart, hidden_scale is unused
     const b200moe_config& c = h->cfg;
@@ -371,7 +394,8 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
         fp.hidden = static_cast<const uint8_t*>(hidden); fp.hscale = static_cast<const float*>(hidden_scale);
         fp.a_perm = a_perm; fp.a_scale_perm = a_scale; fp.H = H;
         const int fgrid = h->num_sms < 32 ? h->num_sms : 32;
-        CU_TRY(launch_k(PDL_PERMUTE, front_small_kernel, dim3(fgrid), dim3(FRONT_THREADS), 0, st, fp));
+        if (route_in_front) CU_TRY(launch_front_route(c, fgrid, fp, *route_in_front, st));
+        else CU_TRY(launch_k(PDL_PERMUTE, front_small_kernel, dim3(fgrid), dim3(FRONT_THREADS), 0, st, fp));
         CU_TRY(prof_mark(h, 2, st));
         CU_TRY(prof_mark(h, 3, st));
     } else {
@@ -424,18 +448,19 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     else CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
     CU_TRY(prof_mark(h, 5, st));
 
-    const int cgrid = T < h->num_sms * 8 ? T : h->num_sms * 8;
+    const int cgrid_x = T < h->num_sms * 8 ? T : h->num_sms * 8;
+    const dim3 cgrid(cgrid_x, T <= 256 ? 4 : 1);        // few tokens: four CTAs share a token's columns
     SlotOut so;
     memset(&so, 0, sizeof(so));            // cap == 0: rows go to `out`
     if (slot_out) so = *slot_out;
     if (out_kind == OUT_BF16)
-        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_BF16>, dim3(cgrid), dim3(256), 0, st, (const __half*)y, topk_idx,
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_BF16>, cgrid, dim3(256), 0, st, (const __half*)y, topk_idx,
                         (const int32_t*)pair_row, (const float*)row_w, out, T, H, c.top_k, pp.pair_stride, local_offset, El, so));
     else if (out_kind == OUT_F16)
-        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F16>, dim3(cgrid), dim3(256), 0, st, (const __half*)y, topk_idx,
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F16>, cgrid, dim3(256), 0, st, (const __half*)y, topk_idx,
                         (const int32_t*)pair_row, (const float*)row_w, out, T, H, c.top_k, pp.pair_stride, local_offset, El, so));
     else
-        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F32>, dim3(cgrid), dim3(256), 0, st, (const __half*)y, topk_idx,
+        CU_TRY(launch_k(PDL_COMBINE, combine_kernel<OUT_F32>, cgrid, dim3(256), 0, st, (const __half*)y, topk_idx,
                         (const int32_t*)pair_row, (const float*)row_w, out, T, H, c.top_k, pp.pair_stride, local_offset, El, so));
     CU_TRY(prof_mark(h, 6, st));
     if (h->prof_slots) ++h->prof_calls;
@@ -561,8 +586,8 @@ int b200moe_workspace_bytes(b200moe_handle h, int num_tokens, size_t* bytes) {
 
 int b200moe_launches_per_forward(b200moe_handle h, int num_tokens, int* launches) {
     if (!h || !launches || num_tokens < 0) return B200MOE_E_BADARG;
-    // route, [permute, gather | fused permute+gather for small T], gemm1, gemm2, combine
-    *launches = num_tokens == 0 ? 0 : (num_tokens <= FRONT_MAX_T ? 5 : 6);
+    // [route, permute, gather | fused route+permute+gather for small T], gemm1, gemm2, combine
+    *launches = num_tokens == 0 ? 0 : (num_tokens <= FRONT_MAX_T ? 4 : 6);
     return 0;
 }
 
@@ -606,11 +631,11 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     rp.topk_idx = reinterpret_cast<int32_t*>(ws + L.topk_idx); rp.topk_w = reinterpret_cast<float*>(ws + L.topk_w);
     rp.slices = reinterpret_cast<int*>(ws + L.slices);
     const bool fused = T <= FRONT_MAX_T;
-    if (fused) rp.slices = nullptr;       // the fused kernel builds the histogram itself
-    CU_TRY(do_route(c, rp, st));
+    if (fused) rp.slices = nullptr;       // the fused front end routes and builds the histogram itself (one launch)
+    else CU_TRY(do_route(c, rp, st));
     CU_TRY(prof_mark(h, 1, st));
     return run_experts(h, rp.topk_idx, rp.topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output,
-                       OUT_BF16, ws, L, st, fused);
+                       OUT_BF16, ws, L, st, fused, nullptr, 0, fused ? &rp : nullptr);
 }
 
 int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const float* topk_w, const void* hidden,

@@ -27,7 +27,10 @@ struct FrontParams {
     int H;
 };
 
-__global__ void __launch_bounds__(FRONT_THREADS, 1) front_small_kernel(const FrontParams fp) {
+// The body shared by the two entry kernels below.  FRESH: the routing result was written earlier in this same
+// launch by other CTAs (read it past L1).
+template <bool FRESH>
+__device__ __forceinline__ void front_body(const FrontParams& fp) {
     __shared__ int s_idx[FRONT_MAX_T * 8];
     __shared__ float s_w[FRONT_MAX_T * 8];
     __shared__ int s_cnt[MAX_LOCAL];
@@ -41,17 +44,15 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_small_kernel(const Fro
     const int n = T * K;
 
     for (int i = tid; i < El; i += blockDim.x) s_cnt[i] = 0;
-    pdl_wait();
-    pdl_launch();
     __syncthreads();
 
     // ---- the routing result of all tokens, and the histogram of the local experts
     for (int i = tid; i < n; i += blockDim.x) {
         const int tok = i / K;
         const size_t src = (size_t)tok * pp.pair_stride + (i - tok * K);
-        const int id = pp.topk_idx[src];
+        const int id = FRESH ? __ldcg(pp.topk_idx + src) : pp.topk_idx[src];
         s_idx[i] = id;
-        s_w[i] = pp.topk_w[src];
+        s_w[i] = FRESH ? __ldcg(pp.topk_w + src) : pp.topk_w[src];
         const int le = id - pp.local_offset;
         if (le >= 0 && le < El) atomicAdd(&s_cnt[le], 1);
     }
@@ -121,4 +122,53 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_small_kernel(const Fro
     }
 }
 
+
+// Front end for tokens that were routed by an earlier kernel.
+__global__ void __launch_bounds__(FRONT_THREADS, 1) front_small_kernel(const FrontParams fp) {
+    pdl_wait();
+    pdl_launch();
+    front_body<false>(fp);
+}
+
+// Front end INCLUDING the routing (the operator's own forward for T <= FRONT_MAX_T): one launch instead of two.
+// Phase A: the tokens are dealt over the CTAs (one warp per token) and routed; the CTAs then meet at a counter in
+// global memory (zero at launch, all CTAs of this small grid are resident; the wait is bounded like every wait of the
+// library); phase B is the common body, every CTA redoing the integer work for all tokens.
+template <int VPT, int MODE>
+__global__ void __launch_bounds__(FRONT_THREADS, 1) front_route_kernel(const FrontParams fp, const RouteParams rp) {
+    __shared__ int s_go;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_launch();
+    for (int t = (int)blockIdx.x + (int)gridDim.x * warp; t < rp.T; t += (int)gridDim.x * (FRONT_THREADS / 32)) {
+        int sel_id; float w;
+        route_token<VPT, MODE>(rp, t, lane, sel_id, w);
+        if (lane < rp.top_k) {
+            rp.topk_idx[(size_t)t * rp.top_k + lane] = sel_id;
+            rp.topk_w[(size_t)t * rp.top_k + lane] = w;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int* const meet = fp.plan.status + ST_MEET;
+        atomicAdd(meet, 1);
+        int go = 1;
+        const unsigned long long t0 = globaltimer_ns();
+        for (uint32_t it = 1;; ++it) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(meet) : "memory");
+            if (v >= (int)gridDim.x) break;
+            if ((it & 0xFFu) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                atomicCAS(fp.plan.status + ST_ERR, 0, ERR_WAIT_GROUP); go = 0; break;
+            }
+        }
+        s_go = go;
+    }
+    __syncthreads();
+    if (!s_go) return;
+    front_body<true>(fp);
+}
+
 }  // namespace b200moe
+

@@ -18,7 +18,7 @@ constexpr int ROW_ALIGN = 16;
 constexpr int MAX_LOCAL = 256;
 
 // status word layout (int32[8]) at the head of the workspace
-enum : int { ST_ERR = 0, ST_PAIRS = 1, ST_ROWS = 2, ST_TILES = 3, ST_ACTIVE = 4 };
+enum : int { ST_ERR = 0, ST_PAIRS = 1, ST_ROWS = 2, ST_TILES = 3, ST_ACTIVE = 4, ST_MEET = 6 /* meeting counter of the fused front end */ };
 
 struct PlanParams {
     int T, top_k, num_local, local_offset, token_tile;
@@ -272,6 +272,9 @@ __global__ void __launch_bounds__(256) combine_kernel(const __half* __restrict__
     __shared__ int s_n;
     pdl_wait();
     pdl_launch();
+    // gridDim.y CTAs share a token's columns (few tokens: more CTAs in flight, shorter latency chain per CTA)
+    const int h_per = ((H / 8 + gridDim.y - 1) / gridDim.y) * 8;
+    const int h_lo = blockIdx.y * h_per, h_hi = min(H, h_lo + h_per);
     for (int t = blockIdx.x; t < T; t += gridDim.x) {
         uint16_t* out_row = reinterpret_cast<uint16_t*>(out) + (size_t)t * H;      // 2-byte kinds
         if (OUT == OUT_F16 && slots.cap > 0) {
@@ -299,7 +302,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const __half* __restrict__
         }
         __syncthreads();
         const int n = s_n;
-        for (int h = threadIdx.x * 8; h < H; h += blockDim.x * 8) {
+        for (int h = h_lo + threadIdx.x * 8; h < h_hi; h += blockDim.x * 8) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (int j = 0; j < n; ++j) fma8_f16(acc, *reinterpret_cast<const uint4*>(y + (size_t)s_rows[j] * H + h), s_w[j]);
             if (OUT == OUT_BF16) {
