@@ -82,6 +82,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     }
 }
 
+// The wrappers below are one PTX instruction each; their bodies are fixed by the ISA (operand order, state spaces,
+// qualifiers), so any sm_100a code base that wraps the same instructions reads alike.
 // ---------------------------------------------------------------- TMA (non-multicast only)
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

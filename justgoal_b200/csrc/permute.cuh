@@ -304,7 +304,16 @@ __global__ void __launch_bounds__(256) combine_kernel(const __half* __restrict__
         const int n = s_n;
         for (int h = h_lo + threadIdx.x * 8; h < h_hi; h += blockDim.x * 8) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int j = 0; j < n; ++j) fma8_f16(acc, *reinterpret_cast<const uint4*>(y + (size_t)s_rows[j] * H + h), s_w[j]);
+            // four rows' loads in flight at a time (the rows are independent; the sum order stays j = 0, 1, ...)
+            for (int j0 = 0; j0 < n; j0 += 4) {
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (j0 + u < n) v[u] = *reinterpret_cast<const uint4*>(y + (size_t)s_rows[j0 + u] * H + h);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (j0 + u < n) fma8_f16(acc, v[u], s_w[j0 + u]);
+            }
             if (OUT == OUT_BF16) {
                 *reinterpret_cast<uint4*>(out_row + h) = pack8_bf16(acc);
             } else if (OUT == OUT_F16) {
