@@ -199,7 +199,17 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint8_t* __restrict__
         uint4* dst = reinterpret_cast<uint4*>(a_perm + (size_t)r * H);
         if (t < 0) continue;   // padding rows stay unwritten: their columns are never stored by the GEMMs
         const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * src_pitch);
-        for (int i = lane; i < H / 16; i += 32) dst[i] = __ldg(src + i);
+        // batches of loads before their stores: several 16-byte loads in flight per lane
+        constexpr int GB = 7;
+        for (int i0 = lane; i0 < H / 16; i0 += 32 * GB) {
+            uint4 v[GB];
+#pragma unroll
+            for (int u = 0; u < GB; ++u)
+                if (i0 + 32 * u < H / 16) v[u] = __ldg(src + i0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < GB; ++u)
+                if (i0 + 32 * u < H / 16) dst[i0 + 32 * u] = v[u];
+        }
         if (hscale) {
             for (int kb = lane; kb < KB; kb += 32) a_scale_perm[(size_t)kb * rows_cap + r] = __ldg(hscale + (size_t)kb * T + t);
         } else {
