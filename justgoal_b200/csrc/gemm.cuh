@@ -193,12 +193,13 @@ struct WorkItem { int u, gb, ge, kind, ut, slot, nwait; };
 
 // CTA that owns flat index x when `total` indices are cut into `parts` equal contiguous ranges (part c starts at
 // c * total / parts)
-__device__ __forceinline__ long long range_start(long long c, long long total, long long parts) { return c * total / parts; }
-__device__ __forceinline__ int range_owner(long long x, long long total, long long parts) {
-    long long c = x * parts / total;
+// (32-bit arithmetic: total < #SMs * K groups, parts <= #SMs, so every product stays far below 2^31)
+__device__ __forceinline__ int range_start(int c, int total, int parts) { return (int)((unsigned)c * (unsigned)total / (unsigned)parts); }
+__device__ __forceinline__ int range_owner(int x, int total, int parts) {
+    int c = (int)((unsigned)x * (unsigned)parts / (unsigned)total);
     while (c + 1 < parts && range_start(c + 1, total, parts) <= x) ++c;
     while (c > 0 && range_start(c, total, parts) > x) --c;
-    return (int)c;
+    return c;
 }
 
 // Chunks per chunked unit
@@ -376,22 +377,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             // pieces that do not end their unit come first, then the one that does (it waits for pieces other CTAs
             // run first, so no chain of waiting CTAs can form), then whole units
             const int tail_units = total_units - sched_U0;
-            const long long flat = (long long)tail_units * NG;
-            const long long parts = flat < (long long)gridDim.x ? (flat > 0 ? flat : 1) : (long long)gridDim.x;
-            const bool has_tail = C::STATIC_TAIL && flat > 0 && (long long)blockIdx.x < parts;
-            const long long t_lo = has_tail ? range_start(blockIdx.x, flat, parts) : 0;
-            const long long t_hi = has_tail ? range_start(blockIdx.x + 1, flat, parts) : 0;
-            int st_pass = has_tail ? 0 : 3, st_ut = (int)(t_lo / NG);
+            const int flat = tail_units * NG;
+            const int parts = flat < (int)gridDim.x ? (flat > 0 ? flat : 1) : (int)gridDim.x;
+            const bool has_tail = C::STATIC_TAIL && flat > 0 && (int)blockIdx.x < parts;
+            const int t_lo = has_tail ? range_start((int)blockIdx.x, flat, parts) : 0;
+            const int t_hi = has_tail ? range_start((int)blockIdx.x + 1, flat, parts) : 0;
+            int st_pass = has_tail ? 0 : 3, st_ut = t_lo / NG;
             while (ok) {
                 WorkItem wi;
                 wi.kind = WK_WHOLE; wi.ut = -1; wi.slot = 0; wi.nwait = 0;
                 bool have = false;
                 while (st_pass < 3 && !have) {
-                    const int ut_last = (int)((t_hi - 1) / NG);
+                    const int ut_last = (t_hi - 1) / NG;
                     while (st_ut <= ut_last && !have) {
                         const int ut = st_ut++;
-                        const long long u_lo = (long long)ut * NG;
-                        const int gb = (int)(max(t_lo, u_lo) - u_lo), ge = (int)(min(t_hi, u_lo + NG) - u_lo);
+                        const int u_lo = ut * NG;
+                        const int gb = max(t_lo, u_lo) - u_lo, ge = min(t_hi, u_lo + NG) - u_lo;
                         const int kind = (gb == 0 && ge == NG) ? WK_WHOLE : (ge == NG ? WK_FINISH : WK_PART);
                         const int want = st_pass == 0 ? WK_PART : (st_pass == 1 ? WK_FINISH : WK_WHOLE);
                         if (kind != want) continue;
@@ -405,7 +406,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         }
                         have = true;
                     }
-                    if (!have) { ++st_pass; st_ut = (int)(t_lo / NG); }
+                    if (!have) { ++st_pass; st_ut = t_lo / NG; }
                 }
                 if (have) {
                 } else if (n_whole < sched_q) {
