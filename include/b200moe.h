@@ -91,8 +91,12 @@ typedef struct b200moe_ws_layout {
 } b200moe_ws_layout;
 
 /* Create / destroy a layer handle on the CURRENT device.  Does one-time kernel attribute
- * setup.  Replaces the one-time setup block of the reference launcher
- * (KF94/kernel.cu:5355-5402) and `moe_init` (SF1/kernel.py:40-44). */
+ * setup and allocates 64 bytes of device memory (two words at which the CTAs of the fused
+ * front end meet; no later call allocates).  Replaces the one-time setup block of the reference
+ * launcher (KF94/kernel.cu:5355-5402) and `moe_init` (SF1/kernel.py:40-44).
+ * Calls that use one handle must be ordered with respect to each other on the GPU (one stream,
+ * or events between streams): b200moe_forward calls for up to 128 tokens share those two words.
+ * Use one handle per stream for forwards that may overlap. */
 int b200moe_create(const b200moe_config* cfg, b200moe_handle* out);
 int b200moe_destroy(b200moe_handle h);
 

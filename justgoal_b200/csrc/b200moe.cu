@@ -38,6 +38,8 @@ struct b200moe_ctx {
     int ablate;                // B200MOE_ABLATE environment variable at create (timing experiments; 0 in normal use)
     unsigned long long wait_limit_ns;   // limit of the waits on a PEER (barrier flags); b200moe_set_wait_limit_ns
     int pair_grid[2];          // CTAs of the SM-pair kernels (GEMM1, GEMM2): 2 x clusters that can be resident; 0 = unusable
+    int* d_sync;               // device, 64 bytes, zero between calls: the meeting words of the fused front end
+                               // (front.cuh).  One forward per handle may be in flight at a time.
 };
 
 namespace {
@@ -393,6 +395,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
         fp.plan = pp;
         fp.hidden = static_cast<const uint8_t*>(hidden); fp.hscale = static_cast<const float*>(hidden_scale);
         fp.a_perm = a_perm; fp.a_scale_perm = a_scale; fp.H = H;
+        fp.sync = h->d_sync; fp.head = reinterpret_cast<uint4*>(ws); fp.head_vec = route_in_front ? (int)(L.expert_row0 / 16) : 0;
         const int fgrid = h->num_sms < 32 ? h->num_sms : 32;
         if (route_in_front) CU_TRY(launch_front_route(c, fgrid, fp, *route_in_front, st));
         else CU_TRY(launch_k(PDL_PERMUTE, front_small_kernel, dim3(fgrid), dim3(FRONT_THREADS), 0, st, fp));
@@ -517,8 +520,16 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     h->cfg = *cfg; h->device = dev; h->num_sms = sms;
     h->prof_slots = 0; h->prof_calls = 0; h->prof_events = nullptr;
     h->wait_limit_ns = WAIT_LIMIT_NS;
+    h->d_sync = nullptr;
+    if (cudaMalloc(&h->d_sync, 64) != cudaSuccess || cudaMemset(h->d_sync, 0, 64) != cudaSuccess) {
+        const cudaError_t e = cudaGetLastError();
+        if (h->d_sync) cudaFree(h->d_sync);
+        delete h;
+        return e != cudaSuccess ? (int)e : (int)cudaErrorMemoryAllocation;
+    }
     int rc_p;
     if ((rc_p = set_attr_pair<true>(sms, &h->pair_grid[0])) || (rc_p = set_attr_pair<false>(sms, &h->pair_grid[1]))) {
+        cudaFree(h->d_sync);
         delete h;
         return rc_p;
     }
@@ -535,6 +546,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
 int b200moe_destroy(b200moe_handle h) {
     if (!h) return B200MOE_E_BADARG;
     b200moe_profile_enable(h, 0);
+    cudaFree(h->d_sync);
     delete h;
     return 0;
 }
@@ -621,8 +633,11 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     set_call_pdl(T);
-    // status, K-split counters and slice histograms are contiguous at the head of the workspace: one memset
-    CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
+    const bool fused = T <= FRONT_MAX_T;
+    // status, K-split counters and slice histograms are contiguous at the head of the workspace: one memset - or none
+    // for small token counts, where the fused front end clears the head itself and can then overlap the kernel the
+    // caller ran before this call
+    if (!fused) CU_TRY(cudaMemsetAsync(ws, 0, L.expert_row0, st));
     CU_TRY(prof_mark(h, 0, st));
     RouteParams rp;
     rp.logits = static_cast<const float*>(logits); rp.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -630,7 +645,6 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     rp.local_offset = local_offset; rp.num_local = c.num_local_experts; rp.scale = scale;
     rp.topk_idx = reinterpret_cast<int32_t*>(ws + L.topk_idx); rp.topk_w = reinterpret_cast<float*>(ws + L.topk_w);
     rp.slices = reinterpret_cast<int*>(ws + L.slices);
-    const bool fused = T <= FRONT_MAX_T;
     if (fused) rp.slices = nullptr;       // the fused front end routes and builds the histogram itself (one launch)
     else CU_TRY(do_route(c, rp, st));
     CU_TRY(prof_mark(h, 1, st));
@@ -900,6 +914,7 @@ int b200moe_status(b200moe_handle h, const void* workspace, void* stream, int* w
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     CU_TRY(cudaMemcpyAsync(word, workspace, sizeof(int), cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));
+    if (*word) CU_TRY(cudaMemset(h->d_sync, 0, 64));      // a front end that gave up at its meeting leaves the words dirty
     return *word ? B200MOE_E_KERNEL : 0;
 }
 

@@ -25,6 +25,13 @@ struct FrontParams {
     uint8_t* a_perm;              // [rows_cap, H]
     float* a_scale_perm;          // [H/128, rows_cap]
     int H;
+    // front_route_kernel only.  `sync` is two words owned by the handle, zero between calls: [0] CTAs that have
+    // arrived at the meeting, [1] CTAs that have left it (the last one to leave clears both).  `head` is the part of
+    // the workspace that must be zero before the GEMMs run (status, split-unit counters), in 16-byte units: CTA 0
+    // clears it, so the forward needs no memset in front of the kernel.
+    int* sync;
+    uint4* head;
+    int head_vec;
 };
 
 // The body shared by the two entry kernels below.  FRESH: the routing result was written earlier in this same
@@ -130,16 +137,35 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_small_kernel(const Fro
     front_body<false>(fp);
 }
 
-// Front end INCLUDING the routing (the operator's own forward for T <= FRONT_MAX_T): one launch instead of two.
+// Front end INCLUDING the routing (the operator's own forward for T <= FRONT_MAX_T): one launch, and nothing else on the
+// stream before it (CTA 0 clears the head of the workspace itself), so the kernel may start while the caller's
+// previous kernel still runs.  Before the wait for that kernel the CTAs pull the inputs into L2 (a prefetch returns
+// no data, so it is harmless if the previous kernel is still writing them; it hides the first-touch latency of
+// every input behind that kernel's tail).
 // Phase A: the tokens are dealt over the CTAs (one warp per token) and routed; the CTAs then meet at a counter in
-// global memory (zero at launch, all CTAs of this small grid are resident; the wait is bounded like every wait of the
-// library); phase B is the common body, every CTA redoing the integer work for all tokens.
+// device memory owned by the handle (all CTAs of this small grid are resident; the wait is bounded like every wait
+// of the library); phase B is the common body, every CTA redoing the integer work for all tokens.
 template <int VPT, int MODE>
 __global__ void __launch_bounds__(FRONT_THREADS, 1) front_route_kernel(const FrontParams fp, const RouteParams rp) {
     __shared__ int s_go;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    {
+        const size_t gtid = (size_t)blockIdx.x * FRONT_THREADS + threadIdx.x, gth = (size_t)gridDim.x * FRONT_THREADS;
+        auto pull = [&](const void* base, size_t bytes) {
+            for (size_t off = gtid * 128; off < bytes; off += gth * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(static_cast<const char*>(base) + off));
+        };
+        pull(rp.logits, (size_t)rp.T * rp.E * 4);
+        pull(fp.hidden, (size_t)rp.T * fp.H);
+        pull(fp.hscale, (size_t)(fp.H >> 7) * rp.T * 4);
+        if (rp.bias) pull(rp.bias, (size_t)rp.E * 2);
+    }
     pdl_wait();
     pdl_launch();
+    // CTA 0 clears the head of the workspace.  Nothing reads or flags an error in it before the meeting below, and
+    // CTA 0 arrives there only after its stores (the fence before the arrival orders them).
+    if (blockIdx.x == 0)
+        for (int i = threadIdx.x; i < fp.head_vec; i += FRONT_THREADS) fp.head[i] = make_uint4(0u, 0u, 0u, 0u);
     for (int t = (int)blockIdx.x + (int)gridDim.x * warp; t < rp.T; t += (int)gridDim.x * (FRONT_THREADS / 32)) {
         int sel_id; float w;
         route_token<VPT, MODE>(rp, t, lane, sel_id, w);
@@ -151,7 +177,7 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_route_kernel(const Fro
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        int* const meet = fp.plan.status + ST_MEET;
+        int* const meet = fp.sync;
         atomicAdd(meet, 1);
         int go = 1;
         const unsigned long long t0 = globaltimer_ns();
@@ -163,6 +189,9 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_route_kernel(const Fro
                 atomicCAS(fp.plan.status + ST_ERR, 0, ERR_WAIT_GROUP); go = 0; break;
             }
         }
+        // every CTA that leaves has seen the full count: the last one to leave clears both words for the next call
+        // (a call that gave up leaves them dirty; b200moe_status() clears them when it reports the error)
+        if (go && atomicAdd(meet + 1, 1) == (int)gridDim.x - 1) { meet[0] = 0; meet[1] = 0; }
         s_go = go;
     }
     __syncthreads();

@@ -134,9 +134,11 @@ struct GemmCfg {
     // stage has landed and release the stage at once, instead of holding it until the group is folded
     static constexpr bool EARLY_SCALES = KPB * NC <= 32 && NPW < 16;
     static constexpr int SLOT_FLOATS = NACCUM * NC * NPT;  // = NACCUM * 128 * NTOK
-    // K blocks per claimed chunk of a split unit: ~128 KB of weights for narrow tiles (a few microseconds of
-    // streaming); wide tiles carry 64-128 KB of partial sums per chunk, so their units are cut into few chunks
-    static constexpr int CHUNK_BLOCKS = NTOK <= 64 ? 8 : 16;
+    // K blocks per claimed chunk of a split unit.  A chunk streams CHUNK_BLOCKS * 32 KB of weights and leaves
+    // 1 KB * NTOK of partial sums: at NTOK / 8 blocks the partial sums are one eighth of the chunk's traffic for every
+    // tile width, and a narrow tile's last few units spread over many CTAs (decode GEMM2: four left-over units become
+    // 32 chunks instead of 8)
+    static constexpr int CHUNK_BLOCKS = NTOK / 8;
     static constexpr int CHUNK_GROUPS = (CHUNK_BLOCKS / KPB) < 1 ? 1 : (CHUNK_BLOCKS / KPB);
     // GEMM1 with narrow tiles has few, long units (decode: 256 units of 3.7 MB for 148 CTAs): there the units left
     // over after the whole rounds are cut into EQUAL contiguous ranges, one per CTA, processed first (claimed

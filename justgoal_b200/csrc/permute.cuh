@@ -16,9 +16,10 @@ namespace b200moe {
 
 constexpr int ROW_ALIGN = 16;
 constexpr int MAX_LOCAL = 256;
+static_assert((ROW_ALIGN & (ROW_ALIGN - 1)) == 0, "row alignment is a power of two");
 
 // status word layout (int32[8]) at the head of the workspace
-enum : int { ST_ERR = 0, ST_PAIRS = 1, ST_ROWS = 2, ST_TILES = 3, ST_ACTIVE = 4, ST_MEET = 6 /* meeting counter of the fused front end */ };
+enum : int { ST_ERR = 0, ST_PAIRS = 1, ST_ROWS = 2, ST_TILES = 3, ST_ACTIVE = 4 };
 
 struct PlanParams {
     int T, top_k, num_local, local_offset, token_tile;
@@ -56,35 +57,40 @@ __global__ void count_kernel(const int32_t* __restrict__ topk_idx, int n, int to
 // status[] when it is not null.  Must be called by the 32 lanes of one warp.
 __device__ __forceinline__ void scan_counts(const int* counts, int num_local, int token_tile, int* s_row0, int* s_tiles,
                                             int* status, int tid) {
+    // Runs once per launch, on a cold instruction cache: the loops stay rolled and the token tile (a power of two)
+    // divides by a shift, so the code is a few dozen instructions instead of eight unrolled copies with divisions.
     const int per = (num_local + 31) / 32;
-    int c[MAX_LOCAL / 32];
+    const int tsh = 31 - __clz(token_tile);
+    const int i0 = tid * per;
     int rows = 0, tiles = 0, pairs = 0, active = 0;
-#pragma unroll
-    for (int k = 0; k < MAX_LOCAL / 32; ++k) {
-        const int i = tid * per + k;
-        c[k] = (k < per && i < num_local) ? counts[i] : 0;
-        rows += (c[k] + ROW_ALIGN - 1) / ROW_ALIGN * ROW_ALIGN;
-        tiles += (c[k] + token_tile - 1) / token_tile;
-        pairs += c[k]; active += c[k] > 0;
+#pragma unroll 1
+    for (int k = 0; k < per; ++k) {
+        const int c = i0 + k < num_local ? counts[i0 + k] : 0;
+        rows += (c + ROW_ALIGN - 1) & ~(ROW_ALIGN - 1);
+        tiles += (c + token_tile - 1) >> tsh;
+        pairs += c; active += c > 0;
     }
     int rows_in = rows, tiles_in = tiles;
+#pragma unroll 1
     for (int off = 1; off < 32; off <<= 1) {
         const int r = __shfl_up_sync(0xFFFFFFFFu, rows_in, off);
         const int t = __shfl_up_sync(0xFFFFFFFFu, tiles_in, off);
         if (tid >= off) { rows_in += r; tiles_in += t; }
     }
+#pragma unroll 1
     for (int off = 16; off; off >>= 1) {
         pairs += __shfl_xor_sync(0xFFFFFFFFu, pairs, off);
         active += __shfl_xor_sync(0xFFFFFFFFu, active, off);
     }
     int r0 = rows_in - rows, t0 = tiles_in - tiles;       // exclusive prefixes of this lane
-#pragma unroll
-    for (int k = 0; k < MAX_LOCAL / 32; ++k) {
-        const int i = tid * per + k;
-        if (k < per && i < num_local) {
+#pragma unroll 1
+    for (int k = 0; k < per; ++k) {
+        const int i = i0 + k;
+        if (i < num_local) {
+            const int c = counts[i];
             s_row0[i] = r0; s_tiles[i] = t0;
-            r0 += (c[k] + ROW_ALIGN - 1) / ROW_ALIGN * ROW_ALIGN;
-            t0 += (c[k] + token_tile - 1) / token_tile;
+            r0 += (c + ROW_ALIGN - 1) & ~(ROW_ALIGN - 1);
+            t0 += (c + token_tile - 1) >> tsh;
         }
     }
     if (tid == 31) {

@@ -42,6 +42,10 @@ __device__ __forceinline__ uint32_t ordered_key(float f) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// exp() in double precision, rounded to float.  One shared copy of the double-precision routine instead of one per
+// call site: the routing runs once per launch on a cold instruction cache, where code size is time.
+__device__ __noinline__ float exp_f64(float x) { return (float)exp((double)x); }
+
 // Routes token t with one warp.  On return lane r < top_k holds selection r: the global expert
 // id in sel_id and its weight in w.
 template <int VPT, int MODE>
@@ -58,7 +62,7 @@ __device__ __forceinline__ void route_token(const RouteParams& p, int t, int lan
     if (MODE == RM_DEEPSEEK) {
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            const float e = (float)exp(-(double)s[i]);
+            const float e = exp_f64(-s[i]);
             s[i] = __fdiv_rn(1.0f, __fadd_rn(1.0f, e));
             const float b = p.bias ? __bfloat162float(p.bias[lane * VPT + i]) : 0.0f;
             v[i] = __fadd_rn(s[i], b);
@@ -96,7 +100,7 @@ __device__ __forceinline__ void route_token(const RouteParams& p, int t, int lan
         for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(FULL, mx, off));
         float sum = 0.f;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) { s[i] = (float)exp((double)__fsub_rn(s[i], mx)); sum += s[i]; }
+        for (int i = 0; i < VPT; ++i) { s[i] = exp_f64(__fsub_rn(s[i], mx)); sum += s[i]; }
         for (int off = 16; off; off >>= 1) sum += __shfl_xor_sync(FULL, sum, off);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) { s[i] = __fdiv_rn(s[i], sum); v[i] = s[i]; }
@@ -144,12 +148,12 @@ __device__ __forceinline__ void route_token(const RouteParams& p, int t, int lan
     } else if (MODE == RM_RENORMALIZE) {
         // softmax over the top_k selected logits; selection 0 is the largest of them
         const float m0 = __shfl_sync(FULL, sel_s, 0);
-        const float e = lane < p.top_k ? (float)exp((double)__fsub_rn(sel_s, m0)) : 0.f;
+        const float e = lane < p.top_k ? exp_f64(__fsub_rn(sel_s, m0)) : 0.f;
         float esum = e;
         for (int off = 16; off; off >>= 1) esum += __shfl_xor_sync(FULL, esum, off);
         w = __fmul_rn(__fdiv_rn(e, esum), p.scale);
     } else if (MODE == RM_LLAMA4) {
-        const float e = (float)exp(-(double)sel_s);
+        const float e = exp_f64(-sel_s);
         w = __fmul_rn(__fdiv_rn(1.0f, __fadd_rn(1.0f, e)), p.scale);
     } else {
         w = (float)((double)p.scale / (double)p.top_k);
