@@ -396,7 +396,10 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
         fp.hidden = static_cast<const uint8_t*>(hidden); fp.hscale = static_cast<const float*>(hidden_scale);
         fp.a_perm = a_perm; fp.a_scale_perm = a_scale; fp.H = H;
         fp.sync = h->d_sync; fp.head = reinterpret_cast<uint4*>(ws); fp.head_vec = route_in_front ? (int)(L.expert_row0 / 16) : 0;
-        const int fgrid = h->num_sms < 32 ? h->num_sms : 32;
+#ifndef B200MOE_FRONT_GRID
+#define B200MOE_FRONT_GRID 32
+#endif
+        const int fgrid = h->num_sms < B200MOE_FRONT_GRID ? h->num_sms : B200MOE_FRONT_GRID;
         if (route_in_front) CU_TRY(launch_front_route(c, fgrid, fp, *route_in_front, st));
         else CU_TRY(launch_k(PDL_PERMUTE, front_small_kernel, dim3(fgrid), dim3(FRONT_THREADS), 0, st, fp));
         CU_TRY(prof_mark(h, 2, st));
@@ -425,6 +428,10 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     static int evf = -1;
     if (evf < 0) { const char* e = getenv("B200MOE_EVICT_FIRST"); evf = e ? atoi(e) : 1; }
     g1.evict_first_weights = evf && ntok < 128;
+    if (route_in_front && !pairs && wire_pitch == 0) {
+        // the fused front end announces the routing result; GEMM1 schedules itself from it (gemm.cuh)
+        g1.routed = status + ST_ROUTED; g1.topk_idx = topk_idx; g1.n_pairs = T * c.top_k; g1.local_offset = local_offset;
+    }
     g1.sk_count = reinterpret_cast<int*>(ws + L.sk_count);
     g1.sk_partial = reinterpret_cast<float*>(ws + L.sk_partial);
     g1.ablate = h->ablate & 0xFF;

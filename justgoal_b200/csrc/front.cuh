@@ -38,12 +38,12 @@ struct FrontParams {
 // launch by other CTAs (read it past L1).
 template <bool FRESH>
 __device__ __forceinline__ void front_body(const FrontParams& fp) {
-    __shared__ int s_idx[FRONT_MAX_T * 8];
-    __shared__ float s_w[FRONT_MAX_T * 8];
     __shared__ int s_cnt[MAX_LOCAL];
     __shared__ int s_row0[MAX_LOCAL + 1];
     __shared__ int s_tiles[MAX_LOCAL + 1];
     __shared__ int s_row_token[FRONT_MAX_ROWS];
+    __shared__ uint8_t s_wcnt[FRONT_THREADS / 32][MAX_LOCAL];    // pairs of expert e among the 32 pairs of warp w
+    static_assert(FRONT_THREADS >= FRONT_MAX_T * 8, "one thread per (token, expert) pair");
     const PlanParams& pp = fp.plan;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int T = pp.T, K = pp.top_k, El = pp.num_local;
@@ -51,22 +51,32 @@ __device__ __forceinline__ void front_body(const FrontParams& fp) {
     const int n = T * K;
 
     for (int i = tid; i < El; i += blockDim.x) s_cnt[i] = 0;
+    for (int i = tid; i < (int)(sizeof(s_wcnt) / 4); i += blockDim.x) reinterpret_cast<uint32_t*>(s_wcnt)[i] = 0u;
     __syncthreads();
 
-    // ---- the routing result of all tokens, and the histogram of the local experts
-    for (int i = tid; i < n; i += blockDim.x) {
-        const int tok = i / K;
-        const size_t src = (size_t)tok * pp.pair_stride + (i - tok * K);
-        const int id = FRESH ? __ldcg(pp.topk_idx + src) : pp.topk_idx[src];
-        s_idx[i] = id;
-        s_w[i] = FRESH ? __ldcg(pp.topk_w + src) : pp.topk_w[src];
-        const int le = id - pp.local_offset;
-        if (le >= 0 && le < El) atomicAdd(&s_cnt[le], 1);
+    // ---- this thread's pair (pair i = tid, token-major), the histogram of the local experts, and the pair's rank
+    // among the pairs of the same expert inside its warp (stable: pair order)
+    const int tok = tid / K;
+    const bool valid = tid < n;
+    const size_t src = (size_t)tok * pp.pair_stride + (tid - tok * K);
+    const int id = valid ? (FRESH ? __ldcg(pp.topk_idx + src) : pp.topk_idx[src]) : -1;
+    const float wgt = valid ? (FRESH ? __ldcg(pp.topk_w + src) : pp.topk_w[src]) : 0.f;
+    const int le = id - pp.local_offset;
+    const bool local = valid && le >= 0 && le < El;
+    const unsigned same = __match_any_sync(0xFFFFFFFFu, local ? le : -1 - lane);
+    const int rank = __popc(same & ((1u << lane) - 1u));
+    if (local && rank == 0) {
+        s_wcnt[warp][le] = (uint8_t)__popc(same);
+        atomicAdd(&s_cnt[le], __popc(same));
     }
     __syncthreads();
 
     // ---- scan
     if (warp == 0) scan_counts(s_cnt, El, pp.token_tile, s_row0, s_tiles, publish ? pp.status : nullptr, lane);
+    // pairs of the same expert in the warps before this one (independent byte loads, no second scan phase)
+    int before = 0;
+    if (local)
+        for (int w2 = 0; w2 < warp; ++w2) before += s_wcnt[w2][le];
     __syncthreads();
     const int total_rows = min(min(s_row0[El], FRONT_MAX_ROWS), pp.rows_cap);
     if (publish) {
@@ -79,25 +89,14 @@ __device__ __forceinline__ void front_body(const FrontParams& fp) {
     for (int r = tid; r < total_rows; r += blockDim.x) s_row_token[r] = -1;
     __syncthreads();
 
-    // ---- stable permutation: a warp places one expert's pairs in token order (ballot ranks)
-    for (int e = warp; e < El; e += FRONT_THREADS / 32) {
-        if (s_cnt[e] == 0) continue;
-        const int ge = e + pp.local_offset;
-        int placed = 0;
-        for (int base = 0; base < n; base += 32) {
-            const int i = base + lane;
-            const bool hit = i < n && s_idx[i] == ge;
-            const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
-            if (hit) {
-                const int r = s_row0[e] + placed + __popc(m & ((1u << lane) - 1u));
-                if (r < FRONT_MAX_ROWS && r < pp.rows_cap) {
-                    s_row_token[r] = i / K;
-                    if (publish) { pp.pair_row[i] = r; pp.row_w[r] = s_w[i]; }
-                } else {                    // repeated expert ids inside a caller-given row: refuse, write nothing
-                    atomicCAS(pp.status + ST_ERR, 0, ERR_BAD_SCHEDULE);
-                }
-            }
-            placed += __popc(m);
+    // ---- stable permutation: an expert's pairs take its rows in pair order
+    if (local) {
+        const int r = s_row0[le] + before + rank;
+        if (r < FRONT_MAX_ROWS && r < pp.rows_cap) {
+            s_row_token[r] = tok;
+            if (publish) { pp.pair_row[tid] = r; pp.row_w[r] = wgt; }
+        } else {                    // more rows than the caller's capacity: refuse, write nothing
+            atomicCAS(pp.status + ST_ERR, 0, ERR_BAD_SCHEDULE);
         }
     }
     __syncthreads();
@@ -109,23 +108,41 @@ __device__ __forceinline__ void front_body(const FrontParams& fp) {
         }
     }
 
-    // ---- gather: a row is cut into GATHER_SPLIT pieces, one warp per piece, dealt round-robin over all warps of
-    // the grid: with a few dozen rows every lane then has 3-4 independent 16-byte loads in flight instead of 14
-    constexpr int GATHER_SPLIT = 4;
+    // ---- gather: a row is cut into pieces, one warp per piece, dealt round-robin over all warps of the grid.  The
+    // number of pieces grows until every warp has one (a few dozen rows: 16 pieces, one 16-byte load per lane); a
+    // warp with more to copy keeps four loads in flight per lane.
     const int H = fp.H, KB = H >> 7, rows_cap = pp.rows_cap;
-    const int chunks = H / 16, per_piece = (chunks + GATHER_SPLIT - 1) / GATHER_SPLIT;
-    const int n_tasks = total_rows * GATHER_SPLIT;
-    for (int task = blockIdx.x * (FRONT_THREADS / 32) + warp; task < n_tasks; task += gridDim.x * (FRONT_THREADS / 32)) {
-        const int r = task / GATHER_SPLIT, piece = task - r * GATHER_SPLIT;
+    const int chunks = H / 16;
+    const int n_warps = (int)gridDim.x * (FRONT_THREADS / 32);
+    int split = 1;
+    while (split < 16 && total_rows * split * 2 <= n_warps) split *= 2;
+    const int per_piece = (chunks + split - 1) / split;
+    const int n_tasks = total_rows * split;
+    for (int task = blockIdx.x * (FRONT_THREADS / 32) + warp; task < n_tasks; task += n_warps) {
+        const int r = task / split, piece = task - r * split;
         const int t = s_row_token[r];
         if (t < 0) continue;     // padding rows stay unwritten: their columns are never stored by the GEMMs
         uint4* dst = reinterpret_cast<uint4*>(fp.a_perm + (size_t)r * H);
         const uint4* src = reinterpret_cast<const uint4*>(fp.hidden + (size_t)t * H);
         const int c_end = min(chunks, (piece + 1) * per_piece);
-        for (int i = piece * per_piece + lane; i < c_end; i += 32) dst[i] = __ldg(src + i);
-        if (piece == 0)
-            for (int kb = lane; kb < KB; kb += 32)
-                fp.a_scale_perm[(size_t)kb * rows_cap + r] = __ldg(fp.hscale + (size_t)kb * T + t);
+        for (int i = piece * per_piece + lane; i < c_end; i += 128) {
+            uint4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i + 32 * j < c_end) v[j] = __ldg(src + i + 32 * j);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (i + 32 * j < c_end) dst[i + 32 * j] = v[j];
+        }
+        if (piece == split - 1) {
+            // the row's block scales (KB <= 64 for every supported hidden size up to 8192: two loads per lane)
+            for (int kb = lane; kb < KB; kb += 64) {
+                const float s0 = __ldg(fp.hscale + (size_t)kb * T + t);
+                const float s1 = kb + 32 < KB ? __ldg(fp.hscale + (size_t)(kb + 32) * T + t) : 0.f;
+                fp.a_scale_perm[(size_t)kb * rows_cap + r] = s0;
+                if (kb + 32 < KB) fp.a_scale_perm[(size_t)(kb + 32) * rows_cap + r] = s1;
+            }
+        }
     }
 }
 
@@ -161,11 +178,16 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_route_kernel(const Fro
         if (rp.bias) pull(rp.bias, (size_t)rp.E * 2);
     }
     pdl_wait();
-    pdl_launch();
-    // CTA 0 clears the head of the workspace.  Nothing reads or flags an error in it before the meeting below, and
-    // CTA 0 arrives there only after its stores (the fence before the arrival orders them).
-    if (blockIdx.x == 0)
+    // CTA 0 clears the head of the workspace.  Nothing flags an error in it before the meeting below, and CTA 0
+    // arrives there only after its stores (the fence before the arrival orders them).  The next kernel (GEMM1) reads
+    // the ST_ROUTED word of the head before this kernel has completed, so CTA 0 lets it start only when the zeros
+    // are visible.
+    if (blockIdx.x == 0) {
         for (int i = threadIdx.x; i < fp.head_vec; i += FRONT_THREADS) fp.head[i] = make_uint4(0u, 0u, 0u, 0u);
+        __threadfence();
+        __syncthreads();
+    }
+    pdl_launch();
     for (int t = (int)blockIdx.x + (int)gridDim.x * warp; t < rp.T; t += (int)gridDim.x * (FRONT_THREADS / 32)) {
         int sel_id; float w;
         route_token<VPT, MODE>(rp, t, lane, sel_id, w);
@@ -192,6 +214,11 @@ __global__ void __launch_bounds__(FRONT_THREADS, 1) front_route_kernel(const Fro
         // every CTA that leaves has seen the full count: the last one to leave clears both words for the next call
         // (a call that gave up leaves them dirty; b200moe_status() clears them when it reports the error)
         if (go && atomicAdd(meet + 1, 1) == (int)gridDim.x - 1) { meet[0] = 0; meet[1] = 0; }
+        // every CTA fenced its routing results before it arrived and this thread has acquired the full count: whoever
+        // acquires the word below sees the routing of all tokens (GEMM1 builds its schedule from it and starts to
+        // stream weights while this kernel still permutes and gathers)
+        if (go && blockIdx.x == 0)
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(fp.plan.status + ST_ROUTED), "r"(1) : "memory");
         s_go = go;
     }
     __syncthreads();

@@ -69,6 +69,13 @@ struct GemmParams {
     long long* klog;      // [4][KLOG_N]: CTA 0's clock at its first KLOG_N K blocks: TMA issue, data seen by the
                           // MMA warp, group seen by the promotion warps, group folded (hand-back)
     long long* trace;     // [gridDim.x][TRACE_SLOTS]: slot 0 = %globaltimer at entry, others = SM clocks since entry
+    // GEMM1 after the fused front end (small token counts), else null: the front end sets *routed to 1 when the routing
+    // result of all tokens is visible.  The CTAs then build the expert tables themselves from topk_idx (the same
+    // histogram and scan as the front end) and the producer streams the first weight tiles while the front end still
+    // permutes and gathers; the token rows are loaded after the front end has completed.
+    const int* routed;
+    const int32_t* topk_idx;      // [n_pairs] global expert ids (pair_stride == top_k on this path)
+    int n_pairs, local_offset;
     int ablate;           // timing experiments only, builds with -DB200MOE_ENABLE_ABLATE (results are wrong when
                           // non-zero): 1 = issue no MMA, 2 = narrow-tile promotion skips tcgen05.ld/FMA, 4 = producer
                           // skips the token-side loads, 8 = the MMA warp consumes the stages alone
@@ -315,16 +322,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     if (warp == 1) { tmem_alloc(smem_u32(s_tmem), C::TMEM_COLS); tmem_relinquish(); }
     // everything above touches only this CTA's shared memory and TMEM; the tables below are
     // written by the kernels before this one
-    pdl_wait();
-    pdl_launch();
-    for (int i = threadIdx.x; i <= p.num_local; i += blockDim.x) {
-        s_tiles[i] = p.tile_prefix[i];
-        s_row0[i] = p.expert_row0[i];
-        s_cnt[i] = i < p.num_local ? p.counts[i] : 0;
+    bool early = false;             // tables built here, before the previous kernel has completed
+    if (G1 && p.routed) {
+        if (threadIdx.x == 0) {
+            int seen = 0;
+            const unsigned long long t0 = globaltimer_ns();
+            for (uint32_t it = 1;; ++it) {
+                asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(p.routed) : "memory");
+                if (seen) break;
+                if ((it & 0xFFu) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) break;     // fall back to the tables
+            }
+            *s_flag = seen;
+        }
+        for (int i = threadIdx.x; i <= p.num_local; i += blockDim.x) s_cnt[i] = 0;
+        __syncthreads();
+        early = *s_flag != 0;
+    }
+    if (early) {
+        for (int i = threadIdx.x; i < p.n_pairs; i += blockDim.x) {
+            const int le = __ldcg(p.topk_idx + i) - p.local_offset;
+            if (le >= 0 && le < p.num_local) atomicAdd(&s_cnt[le], 1);
+        }
+        __syncthreads();
+        if (warp == 0) scan_counts(s_cnt, p.num_local, NTOK, s_row0, s_tiles, nullptr, lane);
+    } else {
+        pdl_wait();
+        for (int i = threadIdx.x; i <= p.num_local; i += blockDim.x) {
+            s_tiles[i] = p.tile_prefix[i];
+            s_row0[i] = p.expert_row0[i];
+            s_cnt[i] = i < p.num_local ? p.counts[i] : 0;
+        }
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // early schedule: the producer (lane 0 of warp 0, the only lane of that warp that works) waits after its first
+    // weight loads; the other warps wait here, before anything that reads the token rows.  The condition is uniform
+    // over a warp on purpose: lanes of one warp that wait would hold the producer lane at their reconvergence point.
+    if (early && warp != 0) pdl_wait();
+    pdl_launch();
     const uint32_t tmem_base = *s_tmem;
     const uint32_t smem_base = smem_u32(smem);
     if (threadIdx.x == 0) stamp(TR_PROLOGUE);
@@ -363,6 +399,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             const uint64_t pol = policy_evict_first();
             int stage = 0; uint32_t phase = 0;
             bool ok = true, issued = false;
+            bool waited = !early;               // early schedule: has this thread waited for the previous kernel yet
             int nk = 0;
             // the producer decides what this CTA does next and publishes it to the other roles
             int n_item = 0, n_whole = 0;
@@ -436,10 +473,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 }
                 const int wrow = un.e * p.rows_per_expert + un.mt * p.unit_rows;
                 const int kb_end = min(p.KB, ge * C::KPB);
-                for (int kb = gb * C::KPB; kb < kb_end; ++kb) {
-                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, p.status, ERR_WAIT_SMEM_EMPTY)) { ok = false; break; }
-                    const uint32_t st = smem_base + stage * C::STAGE_BYTES;
-                    const uint32_t full = bar_full + 8 * stage;
+                auto load_weights = [&](int s_, int kb) {
+                    const uint32_t st = smem_base + s_ * C::STAGE_BYTES;
+                    const uint32_t full = bar_full + 8 * s_;
                     mbar_arrive_expect_tx(full, (kAblate & 4) ? C::NA * C::A_BYTES : C::TX_BYTES);
                     if (p.evict_first_weights) {
                         tma_load_2d_hint(st, &tm_w, kb * 128, wrow, full, pol);
@@ -448,12 +484,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         tma_load_2d(st, &tm_w, kb * 128, wrow, full);
                         tma_load_2d(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full);
                     }
-                    if (!(kAblate & 4)) {
-                        tma_load_2d(st + C::NA * C::A_BYTES, &tm_b0, kb * 128, un.row0, full);
-                        if (!G1) tma_load_2d(st + C::NA * C::A_BYTES + C::B_BYTES, &tm_b1, kb * 128, un.row0, full);
-                        if (C::SCALES_IN_STAGE)
-                            bulk_load(st + C::SC_OFF, p.b_scale + (size_t)kb * p.rows_cap + un.row0, NTOK * 4, full);
-                    }
+                };
+                auto load_tokens = [&](int s_, int kb) {
+                    if (kAblate & 4) return;
+                    const uint32_t st = smem_base + s_ * C::STAGE_BYTES;
+                    const uint32_t full = bar_full + 8 * s_;
+                    tma_load_2d(st + C::NA * C::A_BYTES, &tm_b0, kb * 128, un.row0, full);
+                    if (!G1) tma_load_2d(st + C::NA * C::A_BYTES + C::B_BYTES, &tm_b1, kb * 128, un.row0, full);
+                    if (C::SCALES_IN_STAGE)
+                        bulk_load(st + C::SC_OFF, p.b_scale + (size_t)kb * p.rows_cap + un.row0, NTOK * 4, full);
+                };
+                int kb_first = gb * C::KPB;
+                if (G1 && !waited) {
+                    // early schedule, first item: the (empty) stage ring takes weight tiles while the front end still
+                    // permutes and gathers, then the wait for it, then the token side of the same stages
+                    const int npre = min(C::STAGES, kb_end - kb_first);
+                    for (int i = 0; i < npre; ++i) load_weights(i, kb_first + i);
+                    stamp(TR_TMA_FIRST); issued = true;
+                    pdl_wait();
+                    waited = true;
+                    for (int i = 0; i < npre; ++i) { load_tokens(i, kb_first + i); klog_put(0, nk++); }
+                    kb_first += npre;
+                    stage = npre;
+                    if (stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+                for (int kb = kb_first; kb < kb_end; ++kb) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, p.status, ERR_WAIT_SMEM_EMPTY)) { ok = false; break; }
+                    load_weights(stage, kb);
+                    load_tokens(stage, kb);
                     if (!issued) { stamp(TR_TMA_FIRST); issued = true; }
                     klog_put(0, nk++);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }

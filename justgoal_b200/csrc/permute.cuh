@@ -19,7 +19,8 @@ constexpr int MAX_LOCAL = 256;
 static_assert((ROW_ALIGN & (ROW_ALIGN - 1)) == 0, "row alignment is a power of two");
 
 // status word layout (int32[8]) at the head of the workspace
-enum : int { ST_ERR = 0, ST_PAIRS = 1, ST_ROWS = 2, ST_TILES = 3, ST_ACTIVE = 4 };
+enum : int { ST_ERR = 0, ST_PAIRS = 1, ST_ROWS = 2, ST_TILES = 3, ST_ACTIVE = 4,
+              ST_ROUTED = 5 /* fused front end: 1 once the routing result of every token is visible */ };
 
 struct PlanParams {
     int T, top_k, num_local, local_offset, token_tile;
