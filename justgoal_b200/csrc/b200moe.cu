@@ -396,10 +396,9 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
         fp.hidden = static_cast<const uint8_t*>(hidden); fp.hscale = static_cast<const float*>(hidden_scale);
         fp.a_perm = a_perm; fp.a_scale_perm = a_scale; fp.H = H;
         fp.sync = h->d_sync; fp.head = reinterpret_cast<uint4*>(ws); fp.head_vec = route_in_front ? (int)(L.expert_row0 / 16) : 0;
-#ifndef B200MOE_FRONT_GRID
-#define B200MOE_FRONT_GRID 32
-#endif
-        const int fgrid = h->num_sms < B200MOE_FRONT_GRID ? h->num_sms : B200MOE_FRONT_GRID;
+        // enough warps to route 128 tokens at once and to copy a few dozen rows in one pass, few enough that GEMM1 can
+        // start on most SMs while this kernel runs (16 and 64 CTAs both measured slower at 64 tokens)
+        const int fgrid = h->num_sms < 32 ? h->num_sms : 32;
         if (route_in_front) CU_TRY(launch_front_route(c, fgrid, fp, *route_in_front, st));
         else CU_TRY(launch_k(PDL_PERMUTE, front_small_kernel, dim3(fgrid), dim3(FRONT_THREADS), 0, st, fp));
         CU_TRY(prof_mark(h, 2, st));
