@@ -85,6 +85,9 @@ typedef struct b200moe_ws_layout {
                              %globaltimer at entry, slots 1..11 = SM clocks since entry at:
                              prologue done, first/last TMA issue, first/last MMA, first/last
                              promotion, partial published, partials added, epilogue, exit     */
+    size_t tok_count;     /* int32[T][H/256] (narrow token tiles only, else empty): units that have delivered
+                             a row of token t for output columns [256 j, 256 j + 256) - the combine fused
+                             into the GEMM2 epilogue                                          */
     size_t rows_cap;      /* number of rows the row-indexed buffers hold                   */
     size_t token_tile;    /* tokens per GEMM tile chosen for this T                        */
     size_t total_bytes;
@@ -265,6 +268,14 @@ int b200moe_quantize_1x128(const void* x_bf16, int num_tokens, int hidden, void*
  * The reference returns cudaGetLastError() only (KF94/kernel.cu:5681); its device waits
  * are unbounded, ours give up after a time limit and report here. */
 int b200moe_status(b200moe_handle h, const void* workspace, void* cuda_stream, int* word);
+
+/* Fused combine (off by default).  on != 0: b200moe_forward calls whose token count selects a narrow
+ * token tile (b200moe_ws_layout.token_tile < 128) run without the combine launch - the GEMM2 unit
+ * that delivers a token's last expert row sums the token's rows (same order, same bits as the
+ * combine kernel) and stores the bf16 output; the reference fuses its combine the same way
+ * (KF94/kernel.cu:3692-3708, with bf16 reductions in global memory instead of a fixed-order sum).
+ * Measured slower than the separate kernel at 64 tokens; kept for hosts that count launches. */
+int b200moe_set_fused_combine(b200moe_handle h, int on);
 
 /* How long a kernel of this handle waits for another RANK (the barrier flags of the peer-memory
  * exchange) before it gives up, stores its error code and returns: 2 s by default, 1 ns .. 60 s.

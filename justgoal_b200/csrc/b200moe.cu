@@ -38,6 +38,7 @@ struct b200moe_ctx {
     int ablate;                // B200MOE_ABLATE environment variable at create (timing experiments; 0 in normal use)
     unsigned long long wait_limit_ns;   // limit of the waits on a PEER (barrier flags); b200moe_set_wait_limit_ns
     int pair_grid[2];          // CTAs of the SM-pair kernels (GEMM1, GEMM2): 2 x clusters that can be resident; 0 = unusable
+    int fuse_combine;          // b200moe_set_fused_combine: GEMM2 epilogue adds a token's rows up (narrow tiles); default off
     int* d_sync;               // device, 64 bytes, zero between calls: the meeting words of the fused front end
                                // (front.cuh).  One forward per handle may be in flight at a time.
 };
@@ -164,6 +165,8 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     L->counts = take((size_t)El * 4);
     L->sk_count = take((size_t)2 * (4 * h->num_sms + 4) * 4); // [GEMM1 | GEMM2][4 * grid + 4]; zeroed with the head
     L->slices = take((size_t)num_slices(c, T) * El * 4);      // zeroed with the head
+    // narrow token tiles: the combine is fused into GEMM2 and counts row deliveries per (token, 256 output columns)
+    L->tok_count = take(pick_token_tile(c, T) < 128 ? (size_t)T * ((c.hidden + 255) / 256) * 4 : 0);   // zeroed with the head
     L->expert_row0 = take((size_t)(El + 1) * 4);
     L->tile_prefix = take((size_t)(El + 1) * 4);
     L->topk_idx = take((size_t)T * K * 4);
@@ -353,7 +356,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
                 const void* hidden_scale, const void* w13, const void* s13, const void* w2, const void* s2, int T,
                 int local_offset, void* out, int out_kind, uint8_t* ws, const b200moe_ws_layout& L, cudaStream_t st,
                 bool fused_front = false, const SlotOut* slot_out = nullptr, int wire_pitch = 0,
-                const RouteParams* route_in_front = nullptr) {
+                const RouteParams* route_in_front = nullptr, bool allow_fuse = false) {
     // wire_pitch > 0: the tokens are packed dispatch rows read in place - `hidden` points at the first row,
     // topk_idx / topk_w at the ids / weights inside it, rows are wire_pitch bytes apart, hidden_scale is unused
     const b200moe_config& c = h->cfg;
@@ -453,10 +456,26 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g2.ablate = (h->ablate >> 8) & 0xFF;
     g2.trace = g1.trace + (size_t)h->num_sms * TRACE_SLOTS;
     g2.klog = g1.klog + 8 * KLOG_N;
+    // Optional (b200moe_set_fused_combine): the operator's own forward with narrow token tiles lets the GEMM2 unit that
+    // delivers a token's last row add the token's rows up and write the bf16 output - no combine launch.  Same bits
+    // as combine_kernel; measured 9 us slower per 64-token step (the fence, the delivery atomics and the row loads
+    // sit in the epilogue of every unit, where the separate kernel pays them once), so it is off by default.
+    const bool fuse = h->fuse_combine && allow_fuse && ntok < 128 && !pairs && out_kind == OUT_BF16 && !slot_out && wire_pitch == 0;
+    if (fuse) {
+        g2.fuse_out = static_cast<__nv_bfloat16*>(out);
+        g2.tok_count = reinterpret_cast<int*>(ws + L.tok_count);
+        g2.row_token = row_token; g2.pair_row = pair_row; g2.c_topk = topk_idx; g2.c_stride = pp.pair_stride;
+        g2.top_k = c.top_k; g2.T = T; g2.c_local_offset = local_offset;
+    }
     if (pairs) CU_TRY(launch_gemm_pair<false>(h->pair_grid[1], st, m_w2, m_hi, m_lo, g2));
     else CU_TRY(launch_gemm_ntok<false>(ntok, h->num_sms, st, m_w2, m_hi, m_lo, g2));
     CU_TRY(prof_mark(h, 5, st));
 
+    if (fuse) {
+        CU_TRY(prof_mark(h, 6, st));
+        if (h->prof_slots) ++h->prof_calls;
+        return 0;
+    }
     const int cgrid_x = T < h->num_sms * 8 ? T : h->num_sms * 8;
     const dim3 cgrid(cgrid_x, T <= 256 ? 4 : 1);        // few tokens: four CTAs share a token's columns
     SlotOut so;
@@ -526,6 +545,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     h->cfg = *cfg; h->device = dev; h->num_sms = sms;
     h->prof_slots = 0; h->prof_calls = 0; h->prof_events = nullptr;
     h->wait_limit_ns = WAIT_LIMIT_NS;
+    { const char* e = getenv("B200MOE_FUSE_COMBINE"); h->fuse_combine = e ? atoi(e) != 0 : 0; }
     h->d_sync = nullptr;
     if (cudaMalloc(&h->d_sync, 64) != cudaSuccess || cudaMemset(h->d_sync, 0, 64) != cudaSuccess) {
         const cudaError_t e = cudaGetLastError();
@@ -554,6 +574,12 @@ int b200moe_destroy(b200moe_handle h) {
     b200moe_profile_enable(h, 0);
     cudaFree(h->d_sync);
     delete h;
+    return 0;
+}
+
+int b200moe_set_fused_combine(b200moe_handle h, int on) {
+    if (!h) return B200MOE_E_BADARG;
+    h->fuse_combine = on != 0;
     return 0;
 }
 
@@ -604,8 +630,9 @@ int b200moe_workspace_bytes(b200moe_handle h, int num_tokens, size_t* bytes) {
 
 int b200moe_launches_per_forward(b200moe_handle h, int num_tokens, int* launches) {
     if (!h || !launches || num_tokens < 0) return B200MOE_E_BADARG;
-    // [route, permute, gather | fused route+permute+gather for small T], gemm1, gemm2, combine
-    *launches = num_tokens == 0 ? 0 : (num_tokens <= FRONT_MAX_T ? 4 : 6);
+    // [route, permute, gather | fused route+permute+gather for small T], gemm1, gemm2, [combine unless fused into gemm2]
+    const bool fuse = h->fuse_combine && pick_token_tile(h->cfg, num_tokens) < 128 && !use_pairs(h, pick_token_tile(h->cfg, num_tokens));
+    *launches = num_tokens == 0 ? 0 : (num_tokens <= FRONT_MAX_T ? 4 : 6) - (fuse ? 1 : 0);
     return 0;
 }
 
@@ -655,7 +682,7 @@ int b200moe_forward(b200moe_handle h, const void* logits, const void* bias, cons
     else CU_TRY(do_route(c, rp, st));
     CU_TRY(prof_mark(h, 1, st));
     return run_experts(h, rp.topk_idx, rp.topk_w, hidden, hidden_scale, w13, s13, w2, s2, T, local_offset, output,
-                       OUT_BF16, ws, L, st, fused, nullptr, 0, fused ? &rp : nullptr);
+                       OUT_BF16, ws, L, st, fused, nullptr, 0, fused ? &rp : nullptr, true);
 }
 
 int b200moe_forward_routed(b200moe_handle h, const int32_t* topk_idx, const float* topk_w, const void* hidden,

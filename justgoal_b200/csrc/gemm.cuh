@@ -76,6 +76,15 @@ struct GemmParams {
     const int* routed;
     const int32_t* topk_idx;      // [n_pairs] global expert ids (pair_stride == top_k on this path)
     int n_pairs, local_offset;
+    // GEMM2 with the combine fused into its epilogue (narrow token tiles of the operator's own forward), else
+    // fuse_out == null.  tok_count[t * n_mtiles + mt] (zero at launch) counts the units that have stored the columns
+    // [256 mt, 256 mt + 256) of one of token t's rows; the warp that brings it to the number of the token's local
+    // pairs adds those rows up (permute.cuh, combine_token_slab) and writes the bf16 output.  Tokens without a local
+    // pair get their zero row from the otherwise idle warps 2-3.
+    __nv_bfloat16* fuse_out;
+    int* tok_count;
+    const int32_t* row_token; const int32_t* pair_row; const int32_t* c_topk;
+    int c_stride, top_k, T, c_local_offset;
     int ablate;           // timing experiments only, builds with -DB200MOE_ENABLE_ABLATE (results are wrong when
                           // non-zero): 1 = issue no MMA, 2 = narrow-tile promotion skips tcgen05.ld/FMA, 4 = producer
                           // skips the token-side loads, 8 = the MMA warp consumes the stages alone
@@ -618,6 +627,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             stamp(TR_MMA_LAST);
         }
         __syncwarp();
+    } else if (!G1 && p.fuse_out) {
+        // ------------------------------------------------------------ warps 2-3, fused combine: zero rows of the
+        // tokens that have no pair on this rank (nobody else writes them)
+        for (int t = (int)blockIdx.x * 2 + (warp - 2); t < p.T; t += (int)gridDim.x * 2) {
+            bool local = false;
+            if (lane < p.top_k) {
+                const int le = __ldg(p.c_topk + (size_t)t * p.c_stride + lane) - p.c_local_offset;
+                local = le >= 0 && le < p.num_local;
+            }
+            if (__any_sync(0xFFFFFFFFu, local)) continue;
+            uint4* o = reinterpret_cast<uint4*>(p.fuse_out + (size_t)t * p.H);
+            for (int i = lane; i < p.H / 8; i += 32) o[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
     }
     } else {
         // ------------------------------------------------------------ promotion + epilogue
@@ -1037,6 +1059,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         const size_t row = (size_t)(un.row0 + c);
                         p.y[row * p.H + col0] = __float2half_rn(acc[0][i]);
                         if (second) p.y[row * p.H + col0 + p.gate_offset] = __float2half_rn(acc[1][i]);
+                    }
+                }
+                if (p.fuse_out) {
+                    // Fused combine.  The four warps of this column group have now stored all 256 columns of the
+                    // group's NC rows: fence, meet, then count the unit in for every row's token (the group's rows
+                    // are dealt over its warps and lanes, one atomic per row, all in flight together).
+                    __threadfence();
+                    if (!group_sync()) { ok = false; break; }
+                    const int c = c0 + quarter + 4 * lane;
+                    const bool mine = lane < C::NC / 4 && c < un.nvalid;
+                    int t = -1;
+                    bool last = false;
+                    if (mine) {
+                        t = __ldg(p.row_token + un.row0 + c);
+                        int need = 0;
+                        for (int k = 0; k < p.top_k; ++k) {
+                            const int le = __ldg(p.c_topk + (size_t)t * p.c_stride + k) - p.c_local_offset;
+                            need += le >= 0 && le < p.num_local;
+                        }
+                        last = atomicAdd(p.tok_count + (size_t)t * p.n_mtiles + un.mt, 1) == need - 1;
+                    }
+                    unsigned todo = __ballot_sync(0xFFFFFFFFu, last);
+                    if (todo) __threadfence();          // the other units' rows, counted in before this one, are visible
+                    while (todo) {
+                        const int srcl = __ffs(todo) - 1;
+                        todo &= todo - 1;
+                        const int tt = __shfl_sync(0xFFFFFFFFu, t, srcl);
+                        combine_token_slab(p.y, p.c_topk, p.pair_row, p.row_w, p.fuse_out, tt, p.H, p.top_k, p.c_stride,
+                                           p.c_local_offset, p.num_local, un.mt * p.unit_rows, lane);
                     }
                 }
             }

@@ -279,6 +279,55 @@ __device__ __forceinline__ void add8_f16(float* acc, const uint4& v) {
     }
 }
 
+// The combine of ONE token over 256 output columns by one warp (lane l: columns h0 + 8 l .. + 7): the same sum as
+// combine_kernel below - the token's local rows in row order, weight times row in fp32, one rounding to bf16.  Used
+// by the GEMM2 epilogue that delivers a token's last row (gemm.cuh); the rows were written by other CTAs of the same
+// launch, so every load goes to L2 (.cg).
+__device__ __forceinline__ void combine_token_slab(const __half* y, const int32_t* topk_idx, const int32_t* pair_row,
+                                                   const float* row_w, __nv_bfloat16* out, int t, int H, int top_k,
+                                                   int pair_stride, int local_offset, int num_local, int h0, int lane) {
+    const unsigned FULL = 0xFFFFFFFFu;
+    int r = 0x7FFFFFFF;
+    if (lane < top_k) {
+        const int le = __ldcg(topk_idx + (size_t)t * pair_stride + lane) - local_offset;
+        if (le >= 0 && le < num_local) r = __ldcg(pair_row + (size_t)t * top_k + lane);
+    }
+    const float w = r != 0x7FFFFFFF ? __ldcg(row_w + r) : 0.f;
+    int rank = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int rj = __shfl_sync(FULL, r, j);
+        rank += (rj < r) || (rj == r && j < lane);
+    }
+    const int n = __popc(__ballot_sync(FULL, r != 0x7FFFFFFF));
+    int rs = 0; float ws = 0.f;                // lane j < n: the j-th row in row order and its weight
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int rj = __shfl_sync(FULL, r, j);
+        const float wj = __shfl_sync(FULL, w, j);
+        const int kj = __shfl_sync(FULL, rank, j);
+        if (rj != 0x7FFFFFFF && kj == lane) { rs = rj; ws = wj; }
+    }
+    const int h = h0 + lane * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j0 = 0; j0 < n; j0 += 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (j0 + u < n) {
+                const int row = __shfl_sync(FULL, rs, j0 + u);
+                if (h < H) v[u] = __ldcg(reinterpret_cast<const uint4*>(y + (size_t)row * H + h));
+            }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (j0 + u < n) {
+                const float wu = __shfl_sync(FULL, ws, j0 + u);
+                if (h < H) fma8_f16(acc, v[u], wu);
+            }
+    }
+    if (h < H) *reinterpret_cast<uint4*>(out + (size_t)t * H + h) = pack8_bf16(acc);
+}
+
 template <int OUT>
 __global__ void __launch_bounds__(256) combine_kernel(const __half* __restrict__ y, const int32_t* __restrict__ topk_idx,
                                                       const int32_t* __restrict__ pair_row, const float* __restrict__ row_w,

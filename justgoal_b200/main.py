@@ -101,6 +101,11 @@ class MoELayer:
         _lib.check(_lib.lib.b200moe_profile_read(self._h, int(slot), ms), "b200moe_profile_read")
         return dict(zip(self.STAGES, [float(x) for x in ms]))
 
+    def set_fused_combine(self, on: bool):
+        """Narrow token tiles only: let the GEMM2 epilogue add a token's rows up instead of a combine launch (same
+        bits; off by default, measured slower at 64 tokens)."""
+        _lib.check(_lib.lib.b200moe_set_fused_combine(self._h, 1 if on else 0), "b200moe_set_fused_combine")
+
     def set_wait_limit(self, seconds: float):
         """Limit of this layer's waits on another rank (barrier flags of the peer-memory exchange)."""
         _lib.check(_lib.lib.b200moe_set_wait_limit_ns(self._h, int(seconds * 1e9)), "b200moe_set_wait_limit_ns")

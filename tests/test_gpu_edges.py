@@ -119,6 +119,35 @@ def test_small_forwards_back_to_back_without_a_host_wait():
         assert all(torch.equal(same[0].view(torch.int16), o.view(torch.int16)) for o in same[1:])
 
 
+@pytest.mark.parametrize("shape_name,T,tile", [("TINY_DS", 64, 16), ("TINY_DS", 150, 32), ("TINY_DS", 400, 64),
+                                               ("TINY_RENORM", 20, 16), ("TINY_RENORM", 130, 32)])
+def test_fused_combine_equals_the_combine_kernel_bit_for_bit(shape_name, T, tile):
+    """With the fused combine switched on and narrow token tiles the forward has no combine launch: the GEMM2 unit
+    that delivers a token's last row sums the token's rows in its epilogue.  forward_routed keeps the separate combine kernel; both add the same
+    rows in the same order, so the bf16 outputs must be identical - including tokens without a local expert (zero
+    rows) and a hidden size that is not a multiple of 256 (TINY_RENORM: the last unit has one weight tile)."""
+    from justgoal_b200 import MoELayer
+    shape = getattr(I, shape_name)
+    d = I.make_inputs(shape, T, seed=70 + T)
+    layer = MoELayer(shape)
+    assert layer.launches_per_forward(T) == (4 if T <= 128 else 6)
+    layer.set_fused_combine(True)                      # off by default
+    assert layer.launches_per_forward(T) == (3 if T <= 128 else 5)
+    _, out = _forward(shape, d, layer)
+    assert int(layer.layout(T).token_tile) == tile
+    _check_output(shape, d, out)
+    K = shape.top_k
+    idx = layer.view(T, "topk_idx", torch.int32, (T, K)).clone()
+    w = layer.view(T, "topk_w", torch.float32, (T, K)).clone()
+    dc = util.to_cuda(d)
+    out2 = layer.forward_routed(idx, w, dc["hidden_states"], dc["hidden_states_scale"], dc["gemm1_weights"],
+                                dc["gemm1_weights_scale"], dc["gemm2_weights"], dc["gemm2_weights_scale"],
+                                int(d["local_expert_offset"]), out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    assert layer.status(T) == 0
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+
+
 def test_workspace_reuse_across_sizes():
     """One layer object, shrinking and growing token counts back to back (workspace buckets, stale
     tables from the larger call must not leak into the smaller one)."""
