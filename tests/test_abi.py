@@ -33,7 +33,7 @@ def test_strerror_and_struct_sizes():
     assert b"workspace" in _lib.lib.b200moe_strerror(-2)
     assert _lib.lib.b200moe_strerror(0) == b"ok"
     assert ctypes.sizeof(_lib.Config) == 8 * 4
-    assert ctypes.sizeof(_lib.WsLayout) == 22 * ctypes.sizeof(ctypes.c_size_t)
+    assert ctypes.sizeof(_lib.WsLayout) == 23 * ctypes.sizeof(ctypes.c_size_t)
 
 
 def test_null_arguments_are_rejected_without_a_device():
