@@ -23,7 +23,6 @@
 // along K into CHUNKS of a few K blocks, and the CTAs CLAIM those chunks one at a time from a counter in global
 // memory: SMs do not stream at the same rate under full load, and a CTA that finishes early simply takes more
 // chunks (with equal static shares the finish times of the CTAs spread by 7-10 % of the kernel).  A chunked
-// unit is finished by whichever CTA delivers its last chunk: every chunk's fp32 partial goes to its own slot,
 // unit is finished by the CTA that runs its LAST chunk: every other chunk stores its fp32 partial to its own slot
 // and counts itself in with a release; the finisher waits (bounded) for that count, adds the slots in CHUNK order
 // (a fixed order: results are bit-identical from run to run) and runs the epilogue.  Chunks are claimed in order, so
@@ -31,8 +30,14 @@
 // Inside a CTA the producer claims the work and hands it to the MMA and promotion warps through a small queue
 // in shared memory.
 //
+// Small token counts (GemmParams::routed): GEMM1 follows a front-end kernel that routes, permutes and gathers in one
+// launch.  GEMM1's CTAs are resident while it runs; when it announces the routing result they build the expert tables
+// themselves and the producer streams the first weight tiles before the front end has completed - only the token
+// side of those stages waits for it.  Optionally (GemmParams::fuse_out) GEMM2's epilogue also does the combine.
+//
 // Warp roles: warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) + TMEM owner,
-// warps 2-3 idle (they complete the first warpgroup so register re-allocation is legal),
+// warps 2-3 idle (they complete the first warpgroup so register re-allocation is legal; with the fused combine
+// they write the zero rows of tokens that have no pair on this rank),
 // warps 4.. = promotion/epilogue (4 or 8 warps; warp % 4 selects the TMEM lane quarter).
 // Every wait is bounded (common.cuh); no TMA load uses cluster multicast.
 #pragma once
