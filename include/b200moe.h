@@ -277,6 +277,14 @@ int b200moe_status(b200moe_handle h, const void* workspace, void* cuda_stream, i
  * Measured slower than the separate kernel at 64 tokens; kept for hosts that count launches. */
 int b200moe_set_fused_combine(b200moe_handle h, int on);
 
+/* TMA-gathered token rows (off by default).  on != 0: with 128-token tiles GEMM1 reads its token
+ * rows straight from hidden_states (or from the packed dispatch rows) with four-row TMA gathers
+ * (`cp.async.bulk.tensor...tile::gather4`, as KF94/kernel.cu:932-941,3014-3056) through the
+ * token-of-row table, and the activation gather copy is not launched.  Same results bit for bit;
+ * measured three times slower on the GEMM (32 gathers per 128-K block from one producer thread),
+ * so the copy stays the default. */
+int b200moe_set_tma_gather(b200moe_handle h, int on);
+
 /* How long a kernel of this handle waits for another RANK (the barrier flags of the peer-memory
  * exchange) before it gives up, stores its error code and returns: 2 s by default, 1 ns .. 60 s.
  * A rank that stopped between steps then costs its peers one limit, not a hang.  The waits inside
@@ -287,6 +295,8 @@ int b200moe_set_wait_limit_ns(b200moe_handle h, unsigned long long nanoseconds);
 /* Number of this library's kernels one forward over T tokens launches (a count of
  * launches, not of kernels that do useful work). */
 int b200moe_launches_per_forward(b200moe_handle h, int num_tokens, int* launches);
+/* The same count for b200moe_forward_routed / b200moe_forward_routed_slots over num_tokens tokens (slots). */
+int b200moe_launches_routed(b200moe_handle h, int num_tokens, int* launches);
 
 /* Optional stage timing.  enable(slots > 0) creates slots x 7 CUDA events; every forward then
  * records them around its six kernels (slot = call number modulo slots); enable(0) turns it

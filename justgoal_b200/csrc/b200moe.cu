@@ -38,6 +38,7 @@ struct b200moe_ctx {
     int ablate;                // B200MOE_ABLATE environment variable at create (timing experiments; 0 in normal use)
     unsigned long long wait_limit_ns;   // limit of the waits on a PEER (barrier flags); b200moe_set_wait_limit_ns
     int pair_grid[2];          // CTAs of the SM-pair kernels (GEMM1, GEMM2): 2 x clusters that can be resident; 0 = unusable
+    int tma_gather;            // b200moe_set_tma_gather: GEMM1 (128-token tiles) gathers its token rows by TMA; default off
     int fuse_combine;          // b200moe_set_fused_combine: GEMM2 epilogue adds a token's rows up (narrow tiles); default off
     int* d_sync;               // device, 64 bytes, zero between calls: the meeting words of the fused front end
                                // (front.cuh).  One forward per handle may be in flight at a time.
@@ -92,11 +93,11 @@ cudaError_t launch_k(int site, void (*kern)(KArgs...), dim3 grid, dim3 block, si
 }
 
 // 2-D byte tensor [rows][cols] (cols contiguous), box [box_rows][128 bytes], 128-byte swizzle.
-int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint64_t pitch = 0) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return B200MOE_E_DRIVER;
     cuuint64_t dims[2] = {cols, rows};
-    cuuint64_t strides[1] = {cols};
+    cuuint64_t strides[1] = {pitch ? pitch : cols};       // bytes between rows (a multiple of 16)
     cuuint32_t box[2] = {128, box_rows};
     cuuint32_t estr[2] = {1, 1};
     static int promo = -1;
@@ -187,17 +188,17 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     L->total_bytes = off;
 }
 
-template <int NTOK, bool G1>
+template <int NTOK, bool G1, bool G4 = false>
 cudaError_t set_attr() {
     using C = GemmCfg<NTOK, G1>;
     if (C::REALLOC_REGS) {
         // the kernel's setmaxnreg arithmetic assumes the launch allocation; refuse to run otherwise
         cudaFuncAttributes fa;
-        cudaError_t e = cudaFuncGetAttributes(&fa, gemm_kernel<NTOK, G1>);
+        cudaError_t e = cudaFuncGetAttributes(&fa, gemm_kernel<NTOK, G1, G4>);
         if (e != cudaSuccess) return e;
         if (fa.numRegs != C::LAUNCH_REGS) return (cudaError_t)(-B200MOE_E_BUILD + 100000);   // decoded by CU_TRY_ATTR
     }
-    return cudaFuncSetAttribute(gemm_kernel<NTOK, G1>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    return cudaFuncSetAttribute(gemm_kernel<NTOK, G1, G4>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
 }
 
 template <int NTOK, bool G1>
@@ -205,6 +206,13 @@ cudaError_t launch_gemm(int grid, cudaStream_t st, const CUtensorMap& w, const C
                         const GemmParams& p) {
     return launch_k(G1 ? PDL_GEMM1 : PDL_GEMM2, gemm_kernel<NTOK, G1>, dim3(grid), dim3(GemmCfg<NTOK, G1>::NTHREADS),
                     GemmCfg<NTOK, G1>::SMEM_BYTES, st, w, b0, b1, p);
+}
+
+// GEMM1 over 128-token tiles with TMA-gathered token rows
+cudaError_t launch_gemm_g4(int grid, cudaStream_t st, const CUtensorMap& w, const CUtensorMap& b0, const CUtensorMap& b1,
+                           const GemmParams& p) {
+    return launch_k(PDL_GEMM1, gemm_kernel<128, true, true>, dim3(grid), dim3(GemmCfg<128, true>::NTHREADS),
+                    GemmCfg<128, true>::SMEM_BYTES, st, w, b0, b1, p);
 }
 
 template <bool G1>
@@ -381,7 +389,14 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     const bool pairs = use_pairs(h, ntok);
     if ((rc = make_map(&m_w13, w13, (uint64_t)El * 2 * I, H, 128))) return rc;
     if ((rc = make_map(&m_w2, w2, (uint64_t)El * H, I, 128))) return rc;
-    if ((rc = make_map(&m_a, a_perm, rows_cap, H, ntok))) return rc;
+    // Optional (b200moe_set_tma_gather), 128-token tiles: GEMM1 reads the token rows straight from the caller's
+    // activations with four-row TMA gathers through row_token (one-row boxes; rows `pitch` bytes apart when they sit
+    // inside packed dispatch rows) - no gather copy.  Same results; measured three times slower (32 gathers per
+    // 128-K block from one producer thread: ~100 ns each), so the copy stays the default.
+    const bool g4 = ntok == 128 && !pairs && h->tma_gather;
+    if (g4) {
+        if ((rc = make_map(&m_a, hidden, (uint64_t)T, H, 1, wire_pitch > 0 ? (uint64_t)wire_pitch : 0))) return rc;
+    } else if ((rc = make_map(&m_a, a_perm, rows_cap, H, ntok))) return rc;
     if ((rc = make_map(&m_hi, act_hi, rows_cap, I, ntok))) return rc;
     if ((rc = make_map(&m_lo, act_lo, rows_cap, I, ntok))) return rc;
 
@@ -410,6 +425,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
         CU_TRY(launch_k(PDL_PERMUTE, permute_kernel, dim3(num_slices(c, T)), dim3(PERMUTE_THREADS), 0, st, pp));
         CU_TRY(prof_mark(h, 2, st));
 
+        if (!g4) {
         const long long max_rows = (long long)T * (c.top_k < El ? c.top_k : El) + (long long)ROW_ALIGN * El;
         int ggrid = (int)((max_rows + 7) / 8);
         if (ggrid > h->num_sms * 8) ggrid = h->num_sms * 8;
@@ -417,6 +433,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
                         wire_pitch > 0 ? (const float*)nullptr : static_cast<const float*>(hidden_scale),
                         (const int32_t*)row_token, (const int*)status, a_perm, a_scale, T, H, rows_cap,
                         wire_pitch > 0 ? wire_pitch : H));
+        }
         CU_TRY(prof_mark(h, 3, st));
     }
 
@@ -430,6 +447,16 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     static int evf = -1;
     if (evf < 0) { const char* e = getenv("B200MOE_EVICT_FIRST"); evf = e ? atoi(e) : 1; }
     g1.evict_first_weights = evf && ntok < 128;
+    g1.ts_stride = rows_cap;
+    if (g4) {
+        g1.g4_row_token = row_token; g1.g4_T = T;
+        if (wire_pitch > 0) {       // scales follow the fp8 row inside a packed dispatch row
+            g1.g4_scale = reinterpret_cast<const float*>(static_cast<const uint8_t*>(hidden) + H);
+            g1.g4_tok_stride = wire_pitch / 4; g1.ts_stride = 1;
+        } else {                    // the operator's [H/128, T] layout
+            g1.g4_scale = static_cast<const float*>(hidden_scale); g1.g4_tok_stride = 1; g1.ts_stride = T;
+        }
+    }
     if (route_in_front && !pairs && wire_pitch == 0) {
         // the fused front end announces the routing result; GEMM1 schedules itself from it (gemm.cuh)
         g1.routed = status + ST_ROUTED; g1.topk_idx = topk_idx; g1.n_pairs = T * c.top_k; g1.local_offset = local_offset;
@@ -440,6 +467,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g1.trace = reinterpret_cast<long long*>(ws + L.trace);
     g1.klog = g1.trace + (size_t)2 * h->num_sms * TRACE_SLOTS;
     if (pairs) CU_TRY(launch_gemm_pair<true>(h->pair_grid[0], st, m_w13, m_a, m_a, g1));
+    else if (g4) CU_TRY(launch_gemm_g4(h->num_sms, st, m_w13, m_a, m_a, g1));
     else CU_TRY(launch_gemm_ntok<true>(ntok, h->num_sms, st, m_w13, m_a, m_a, g1));
     CU_TRY(prof_mark(h, 4, st));
 
@@ -449,7 +477,7 @@ int run_experts(b200moe_ctx* h, const int32_t* topk_idx, const float* topk_w, co
     g2.KB = I / 128; g2.n_mtiles = (H + 255) / 256; g2.rows_per_expert = H; g2.gate_offset = 128; g2.scale_rows = H / 128;
     g2.unit_rows = 256; g2.valid_rows = H;
     g2.w_scale = static_cast<const float*>(s2); g2.b_scale = act_scale; g2.rows_cap = rows_cap;
-    g2.row_w = row_w; g2.y = y; g2.H = H; g2.I = I;
+    g2.row_w = row_w; g2.y = y; g2.H = H; g2.I = I; g2.ts_stride = rows_cap;
     g2.evict_first_weights = evf && ntok < 128;
     g2.sk_count = reinterpret_cast<int*>(ws + L.sk_count) + 4 * h->num_sms + 4;
     g2.sk_partial = g1.sk_partial;
@@ -538,7 +566,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     CU_TRY_ATTR((set_attr<16, true>()));  CU_TRY_ATTR((set_attr<16, false>()));
     CU_TRY_ATTR((set_attr<32, true>()));  CU_TRY_ATTR((set_attr<32, false>()));
     CU_TRY_ATTR((set_attr<64, true>()));  CU_TRY_ATTR((set_attr<64, false>()));
-    CU_TRY_ATTR((set_attr<128, true>())); CU_TRY_ATTR((set_attr<128, false>()));
+    CU_TRY_ATTR((set_attr<128, true>())); CU_TRY_ATTR((set_attr<128, false>())); CU_TRY_ATTR((set_attr<128, true, true>()));
 #undef CU_TRY_ATTR
     b200moe_ctx* h = new (std::nothrow) b200moe_ctx;
     if (!h) return B200MOE_E_BADARG;
@@ -546,6 +574,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     h->prof_slots = 0; h->prof_calls = 0; h->prof_events = nullptr;
     h->wait_limit_ns = WAIT_LIMIT_NS;
     { const char* e = getenv("B200MOE_FUSE_COMBINE"); h->fuse_combine = e ? atoi(e) != 0 : 0; }
+    { const char* e = getenv("B200MOE_GATHER4"); h->tma_gather = e ? atoi(e) != 0 : 0; }
     h->d_sync = nullptr;
     if (cudaMalloc(&h->d_sync, 64) != cudaSuccess || cudaMemset(h->d_sync, 0, 64) != cudaSuccess) {
         const cudaError_t e = cudaGetLastError();
@@ -574,6 +603,12 @@ int b200moe_destroy(b200moe_handle h) {
     b200moe_profile_enable(h, 0);
     cudaFree(h->d_sync);
     delete h;
+    return 0;
+}
+
+int b200moe_set_tma_gather(b200moe_handle h, int on) {
+    if (!h) return B200MOE_E_BADARG;
+    h->tma_gather = on != 0;
     return 0;
 }
 
@@ -632,7 +667,16 @@ int b200moe_launches_per_forward(b200moe_handle h, int num_tokens, int* launches
     if (!h || !launches || num_tokens < 0) return B200MOE_E_BADARG;
     // [route, permute, gather | fused route+permute+gather for small T], gemm1, gemm2, [combine unless fused into gemm2]
     const bool fuse = h->fuse_combine && pick_token_tile(h->cfg, num_tokens) < 128 && !use_pairs(h, pick_token_tile(h->cfg, num_tokens));
-    *launches = num_tokens == 0 ? 0 : (num_tokens <= FRONT_MAX_T ? 4 : 6) - (fuse ? 1 : 0);
+    const bool g4 = pick_token_tile(h->cfg, num_tokens) == 128 && !use_pairs(h, 128) && h->tma_gather;
+    *launches = num_tokens == 0 ? 0 : (num_tokens <= FRONT_MAX_T ? 4 : 6) - (fuse ? 1 : 0) - (g4 ? 1 : 0);
+    return 0;
+}
+
+int b200moe_launches_routed(b200moe_handle h, int num_tokens, int* launches) {
+    if (!h || !launches || num_tokens < 0) return B200MOE_E_BADARG;
+    // count, [permute + gather | both in one launch for small T; no gather when GEMM1 gathers by TMA], gemm1, gemm2, combine
+    const bool g4 = pick_token_tile(h->cfg, num_tokens) == 128 && !use_pairs(h, 128) && h->tma_gather;
+    *launches = num_tokens == 0 ? 0 : (num_tokens <= FRONT_MAX_T ? 5 : 6) - (g4 ? 1 : 0);
     return 0;
 }
 

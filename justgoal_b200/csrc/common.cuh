@@ -100,6 +100,16 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap
         " [%0], [%1, {%2, %3}], [%4], %5;"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(bar), "l"(policy) : "memory");
 }
+// Four arbitrary rows r0..r3 of a 2-D tensor (map encoded with one-row boxes), columns [x, x + box), land as four
+// consecutive rows at dst (swizzled like a tiled load of the same rows).  A row index outside the tensor reads the
+// fill value (zeros); x must be a multiple of 16 bytes like every TMA coordinate of the innermost dimension.
+__device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const CUtensorMap* m, int x, int r0, int r1, int r2, int r3,
+                                               uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar) : "memory");
+}
 // Untiled bulk copy global -> shared; both addresses 16-byte aligned, size a multiple of 16.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile(

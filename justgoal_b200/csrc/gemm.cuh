@@ -81,6 +81,16 @@ struct GemmParams {
     const int* routed;
     const int32_t* topk_idx;      // [n_pairs] global expert ids (pair_stride == top_k on this path)
     int n_pairs, local_offset;
+    // GEMM1 with 128-token tiles reading the token rows straight from the caller's activations (no gather copy), else
+    // g4_row_token == null: tm_b0 is then a map over the activations with one-row boxes, a stage's token tile is 32
+    // four-row TMA gathers through row_token, and the promotion threads read their token's block scales from the
+    // caller's scale tensor: scale(token, kb) = g4_scale[token * g4_tok_stride + kb * g4_kb_stride].
+    const int32_t* g4_row_token;
+    const float* g4_scale;
+    int g4_tok_stride;    // in floats
+    int g4_T;
+    int ts_stride;        // tokens-on-M tiles: floats between a row's token scales of consecutive K blocks (rows_cap for the
+                          // gathered copy, the caller's K-block stride when g4_row_token is set); K blocks * ts_stride < 2^31
     // GEMM2 with the combine fused into its epilogue (narrow token tiles of the operator's own forward), else
     // fuse_out == null.  tok_count[t * n_mtiles + mt] (zero at launch) counts the units that have stored the columns
     // [256 mt, 256 mt + 256) of one of token t's rows; the warp that brings it to the number of the token's local
@@ -171,7 +181,7 @@ struct GemmCfg {
     static constexpr int TABLE_INTS = 3 * (MAX_LOCAL + 1);
     static constexpr int RED_BYTES = NPW * NC * 4;
     static constexpr int SMEM_BYTES = 1024 /*align slack*/ + STAGES * STAGE_BYTES + BAR_BYTES + WQ * 32 /*work queue*/ +
-                                      TABLE_INTS * 4 + RED_BYTES + 32;
+                                      TABLE_INTS * 4 + RED_BYTES + 32 + 16 + 512 /*token ids of the producer's unit, 16-byte aligned*/;
     static_assert(NTOK % 16 == 0 && NTOK >= 16 && NTOK <= 128, "token tile");
     static_assert(TMEM_COLS >= 32 && TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "tmem");
     static_assert(STAGES >= KPB + 1, "a group must fit the stage ring with room to prefetch");
@@ -280,11 +290,14 @@ __device__ __forceinline__ void tmem_ld_chunk(uint32_t taddr, float* v) {
     for (int i = 0; i < N; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-template <int NTOK, bool G1>
+// G4 (GEMM1 with 128-token tiles only): the token rows come straight from the caller's activations by four-row TMA
+// gathers (GemmParams::g4_row_token); a separate instantiation, so the plain kernel's code is unchanged by it.
+template <int NTOK, bool G1, bool G4 = false>
 __global__ void __launch_bounds__(GemmCfg<NTOK, G1>::NTHREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b0,
             const __grid_constant__ CUtensorMap tm_b1, const GemmParams p) {
     using C = GemmCfg<NTOK, G1>;
+    static_assert(!G4 || (C::TOK_ON_M && G1), "TMA-gathered token rows: GEMM1 with 128-token tiles");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tail = smem + C::STAGES * C::STAGE_BYTES;
@@ -296,6 +309,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     int* s_cnt = s_row0 + (MAX_LOCAL + 1);
     uint32_t* s_red = reinterpret_cast<uint32_t*>(s_cnt + (MAX_LOCAL + 1));
     int* s_flag = reinterpret_cast<int*>(s_red + C::NPW * C::NC);   // [NGRP] arrival order of a split unit, per group
+    // [128] token of every row of the producer's unit, 16-byte aligned (read and written as int4)
+    int* s_g4 = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(s_flag + 8) + 15) & ~uintptr_t(15));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef B200MOE_ENABLE_ABLATE
@@ -499,10 +514,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                         tma_load_2d(st + C::A_BYTES, &tm_w, kb * 128, wrow + p.gate_offset, full);
                     }
                 };
+                constexpr bool g4 = G4;
+                if (g4) {
+                    // tokens of the unit's 128 rows (segments start at multiples of 16 rows: 16-byte loads; rows past
+                    // the expert's own hold other tokens, -1 or stale values - their results are never stored, and a
+                    // row index outside the tensor reads zeros)
+                    const int4* src = reinterpret_cast<const int4*>(p.g4_row_token + un.row0);
+#pragma unroll 1
+                    for (int i = 0; i < 32; ++i) reinterpret_cast<int4*>(s_g4)[i] = __ldg(src + i);
+                }
                 auto load_tokens = [&](int s_, int kb) {
                     if (kAblate & 4) return;
                     const uint32_t st = smem_base + s_ * C::STAGE_BYTES;
                     const uint32_t full = bar_full + 8 * s_;
+                    if (g4) {
+#pragma unroll 1
+                        for (int g = 0; g < 32; ++g) {
+                            const int4 t = reinterpret_cast<const int4*>(s_g4)[g];
+                            tma_gather4_2d(st + C::NA * C::A_BYTES + g * 512, &tm_b0, kb * 128, t.x, t.y, t.z, t.w, full);
+                        }
+                        return;
+                    }
                     tma_load_2d(st + C::NA * C::A_BYTES, &tm_b0, kb * 128, un.row0, full);
                     if (!G1) tma_load_2d(st + C::NA * C::A_BYTES + C::B_BYTES, &tm_b1, kb * 128, un.row0, full);
                     if (C::SCALES_IN_STAGE)
@@ -712,7 +744,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
             }
             // tokens-on-M: this thread's token scale, also one K block ahead (KPB == 1 there)
             const float* tsp = p.b_scale + (size_t)un.row0 + m;
-            float stokn = C::TOK_ON_M ? __ldcg(tsp + (size_t)min(gb * C::KPB, p.KB - 1) * p.rows_cap) : 0.f;
+            if (G4) {
+                const int tok = __ldg(p.g4_row_token + un.row0 + m);
+                tsp = p.g4_scale + (tok >= 0 && tok < p.g4_T ? (size_t)tok * (unsigned)p.g4_tok_stride : 0);   // any finite scale for a row of zeros
+            }
+            float stokn = C::TOK_ON_M ? __ldcg(tsp + (size_t)min(gb * C::KPB, p.KB - 1) * (G4 ? p.ts_stride : p.rows_cap)) : 0.f;
             for (int grp = gb; grp < ge; ++grp) {
                 const int kb0 = grp * C::KPB;
                 const int nj = min(C::KPB, p.KB - kb0);
@@ -725,7 +761,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                     swn[j][1] = __ldg(ws1 + kb);
                 }
                 const float stok_cur = stokn;
-                if (C::TOK_ON_M) stokn = __ldcg(tsp + (size_t)min(kb0 + 1, p.KB - 1) * p.rows_cap);
+                if (C::TOK_ON_M) stokn = __ldcg(tsp + (size_t)min(kb0 + 1, p.KB - 1) * (G4 ? p.ts_stride : p.rows_cap));
                 const int st0 = stage;
                 float scr[C::EARLY_SCALES ? C::KPB : 1][C::EARLY_SCALES ? C::NC : 1];
                 if (C::EARLY_SCALES && !(kAblate & 2)) {

@@ -287,6 +287,7 @@ class ExpertParallelMoE:
         plan = plan_dispatch(idx, s.num_local_experts, self.world, g)
         self.last_plan = plan
         n_recv = sum(plan.recv_counts)
+        self._last_recv = int(n_recv)
         mark("plan")
         # DISPATCH: one packed row per (token, destination rank)
         wire = be.pack(hidden_states, hidden_states_scale, idx, w, plan.send_token)
@@ -307,10 +308,13 @@ class ExpertParallelMoE:
 
     def launches_per_step(self) -> int:
         """Kernels of this library one step launches on one rank.  Peer-memory form: route, push, barrier, count,
-        permute, gather (from the wire slots), GEMM1, GEMM2, combine (stores into the owners' slots), barrier,
-        owner-side sum; collective form: route, pack, unpack, count, permute, gather, GEMM1, GEMM2, combine,
-        owner-side sum."""
-        return 11 if self.peer is not None else 10
+        permute, [gather from the wire slots unless GEMM1 gathers by TMA], GEMM1, GEMM2, combine (stores into the
+        owners' slots), barrier, owner-side sum; collective form: route, pack, unpack, count, permute, [gather],
+        GEMM1, GEMM2, combine, owner-side sum."""
+        if self.peer is not None:       # route, push, barrier | local experts over all slots | barrier, owner-side sum
+            return 5 + self.layer.launches_routed(self.peer.world * self.peer.cap)
+        # route, pack, unpack | local experts over the rows received in the last step | owner-side sum
+        return 4 + self.layer.launches_routed(max(1, getattr(self, "_last_recv", 1)))
 
     def check_status(self):
         """Raises if a barrier of the peer-memory exchange gave up waiting for a peer since the last check (the

@@ -101,6 +101,17 @@ class MoELayer:
         _lib.check(_lib.lib.b200moe_profile_read(self._h, int(slot), ms), "b200moe_profile_read")
         return dict(zip(self.STAGES, [float(x) for x in ms]))
 
+    def launches_routed(self, T: int) -> int:
+        """Kernel launches of forward_routed (or the slot form) over T tokens (slots)."""
+        n = C.c_int(0)
+        _lib.check(_lib.lib.b200moe_launches_routed(self._h, T, C.byref(n)))
+        return n.value
+
+    def set_tma_gather(self, on: bool):
+        """128-token tiles only: GEMM1 gathers its token rows by TMA instead of reading a gathered copy (same bits;
+        off by default, measured slower)."""
+        _lib.check(_lib.lib.b200moe_set_tma_gather(self._h, 1 if on else 0), "b200moe_set_tma_gather")
+
     def set_fused_combine(self, on: bool):
         """Narrow token tiles only: let the GEMM2 epilogue add a token's rows up instead of a combine launch (same
         bits; off by default, measured slower at 64 tokens)."""

@@ -148,6 +148,26 @@ def test_fused_combine_equals_the_combine_kernel_bit_for_bit(shape_name, T, tile
     assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
 
 
+def test_tma_gathered_token_rows_give_the_same_bits():
+    """Optional form of GEMM1 for 128-token tiles: the token rows come from hidden_states by four-row TMA gathers
+    through the token-of-row table instead of from a gathered copy (no gather launch).  Ragged last tiles, padding
+    rows (token -1: the gather reads zeros) and rows of the next expert inside a tile are all in this case."""
+    from justgoal_b200 import MoELayer
+    shape, T = I.TINY_DS, 600
+    d = I.make_inputs(shape, T, seed=91)
+    layer = MoELayer(shape)
+    assert int(layer.layout(T).token_tile) == 128
+    _, out1 = _forward(shape, d, layer)
+    out1 = out1.clone()
+    n1 = layer.launches_per_forward(T)
+    layer.set_tma_gather(True)
+    assert layer.launches_per_forward(T) == n1 - 1
+    layer.workspace(T).fill_(0xFF)          # stale token ids past the last row must be harmless
+    _, out2 = _forward(shape, d, layer)
+    assert torch.equal(out1.view(torch.int16), out2.view(torch.int16))
+    _check_output(shape, d, out2)
+
+
 def test_workspace_reuse_across_sizes():
     """One layer object, shrinking and growing token counts back to back (workspace buckets, stale
     tables from the larger call must not leak into the smaller one)."""
