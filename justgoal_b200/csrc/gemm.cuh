@@ -165,7 +165,8 @@ struct GemmCfg {
     // stage has landed and release the stage at once, instead of holding it until the group is folded
     static constexpr bool EARLY_SCALES = KPB * NC <= 32 && NPW < 16;
     static constexpr int SLOT_FLOATS = NACCUM * NC * NPT;  // = NACCUM * 128 * NTOK
-    // K blocks per claimed chunk of a split unit.  A chunk streams CHUNK_BLOCKS * 32 KB of weights and leaves
+    // SMALLEST number of K blocks per claimed chunk of a split unit (the producer enlarges the chunks when there are
+    // many left-over units: about two chunks per CTA).  A chunk streams CHUNK_BLOCKS * 32 KB of weights and leaves
     // 1 KB * NTOK of partial sums: at NTOK / 8 blocks the partial sums are one eighth of the chunk's traffic for every
     // tile width, and a narrow tile's last few units spread over many CTAs (decode GEMM2: four left-over units become
     // 32 chunks instead of 8)
@@ -400,8 +401,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     const int total_units = s_tiles[p.num_local] * p.n_mtiles;
     const int sched_q = total_units / (int)gridDim.x;              // whole units per CTA
     const int sched_U0 = sched_q * (int)gridDim.x;                 // first chunked unit
-    const int CPU_ = (NG + C::CHUNK_GROUPS - 1) / C::CHUNK_GROUPS; // chunks per chunked unit
-    const int total_chunks = (total_units - sched_U0) * CPU_;
     int* const claim = p.sk_count + 4 * (int)gridDim.x;
 
     // Consumer side of the work queue: item n sits in slot n % WQ.  WARP: every lane of the calling warp waits and
@@ -426,6 +425,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             const uint64_t pol = policy_evict_first();
+            // Chunk size of the left-over units: about two chunks per CTA in total, never below CHUNK_GROUPS groups.  A few
+            // left-over units are cut finely so that every CTA gets a piece; many are cut into two or three chunks each
+            // (every chunk but a unit's last costs a partial-sum slot written and read, and its finisher a wait).
+            {
+                int chunk_groups = C::CHUNK_GROUPS;
+                if (total_units > sched_U0) {
+                    const int per_unit = (2 * (int)gridDim.x + (total_units - sched_U0) - 1) / (total_units - sched_U0);
+                    chunk_groups = max(chunk_groups, (NG + per_unit - 1) / per_unit);
+                }
+                s_flag[4] = chunk_groups;
+                s_flag[5] = (NG + chunk_groups - 1) / chunk_groups;           // chunks per chunked unit
+            }
+            // (kept in shared memory between the rare claims rather than in registers for the whole loop)
+            volatile int* const s_sched = s_flag + 4;
+            const int total_chunks = (total_units - sched_U0) * s_sched[1];
             int stage = 0; uint32_t phase = 0;
             bool ok = true, issued = false;
             bool waited = !early;               // early schedule: has this thread waited for the previous kernel yet
@@ -483,10 +497,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
                 } else {
                     const int c = (!C::STATIC_TAIL && total_chunks > 0) ? atomicAdd(claim, 1) : total_chunks;
                     if (c >= total_chunks) { wi.u = -1; wi.gb = wi.ge = 0; publish(wi); break; }
+                    const int chunk_groups = s_sched[0], CPU_ = s_sched[1];
                     wi.ut = c / CPU_;
                     const int ci = c - wi.ut * CPU_;
                     wi.u = sched_U0 + wi.ut;
-                    wi.gb = ci * C::CHUNK_GROUPS; wi.ge = min(NG, wi.gb + C::CHUNK_GROUPS);
+                    wi.gb = ci * chunk_groups; wi.ge = min(NG, wi.gb + chunk_groups);
                     if (CPU_ > 1) {
                         // chunks are claimed in order: the one that ends the unit is claimed last and finishes it
                         wi.kind = ci + 1 < CPU_ ? WK_PART : WK_FINISH;
