@@ -277,6 +277,13 @@ int b200moe_status(b200moe_handle h, const void* workspace, void* cuda_stream, i
  * Measured slower than the separate kernel at 64 tokens; kept for hosts that count launches. */
 int b200moe_set_fused_combine(b200moe_handle h, int on);
 
+/* Token tile of the GEMMs.  0 (default): chosen from the token count - 16 tokens while an expert
+ * expects about seven rows or fewer, 128 from about nine (measured crossovers on the DeepSeek-V3
+ * shape), 32 in between.  16 / 32 / 64 / 128 force one kernel family for every token count (tuning
+ * and tests; every size gives the same results within the operator's tolerance).  The workspace
+ * size depends on the tile: query b200moe_workspace_bytes again after changing it. */
+int b200moe_set_token_tile(b200moe_handle h, int tokens);
+
 /* TMA-gathered token rows (off by default).  on != 0: with 128-token tiles GEMM1 reads its token
  * rows straight from hidden_states (or from the packed dispatch rows) with four-row TMA gathers
  * (`cp.async.bulk.tensor...tile::gather4`, as KF94/kernel.cu:932-941,3014-3056) through the

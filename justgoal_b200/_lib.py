@@ -56,6 +56,7 @@ def _load():
     lib.b200moe_status.argtypes = [vp, vp, vp, C.POINTER(i)]
     lib.b200moe_set_fused_combine.argtypes = [vp, i]
     lib.b200moe_set_tma_gather.argtypes = [vp, i]
+    lib.b200moe_set_token_tile.argtypes = [vp, i]
     lib.b200moe_launches_per_forward.argtypes = [vp, i, C.POINTER(i)]
     lib.b200moe_launches_routed.argtypes = [vp, i, C.POINTER(i)]
     lib.b200moe_permute_noalloc.argtypes = [vp, vp, vp, i, i, vp, vp, vp, i, vp]
@@ -65,7 +66,7 @@ def _load():
     lib.b200moe_strerror.restype = C.c_char_p
     lib.b200moe_num_sms.argtypes = []
     for name in ("create", "destroy", "workspace_bytes", "workspace_layout", "forward", "route",
-                 "forward_routed", "status", "set_fused_combine", "set_tma_gather", "launches_per_forward", "launches_routed", "num_sms", "profile_enable",
+                 "forward_routed", "status", "set_fused_combine", "set_tma_gather", "set_token_tile", "launches_per_forward", "launches_routed", "num_sms", "profile_enable",
                  "profile_read", "permute_noalloc", "ep_combine", "ep_row_bytes", "ep_pack", "ep_unpack", "ep_push", "ep_barrier", "ep_unpack_slots",
                  "ep_return", "ep_combine_slots", "forward_routed_slots", "quantize_1x128", "set_wait_limit_ns"):
         getattr(lib, "b200moe_" + name).restype = i

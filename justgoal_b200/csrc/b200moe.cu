@@ -38,6 +38,7 @@ struct b200moe_ctx {
     int ablate;                // B200MOE_ABLATE environment variable at create (timing experiments; 0 in normal use)
     unsigned long long wait_limit_ns;   // limit of the waits on a PEER (barrier flags); b200moe_set_wait_limit_ns
     int pair_grid[2];          // CTAs of the SM-pair kernels (GEMM1, GEMM2): 2 x clusters that can be resident; 0 = unusable
+    int token_tile;            // b200moe_set_token_tile: 0 = chosen from the token count, else 16 / 32 / 64 / 128
     int tma_gather;            // b200moe_set_tma_gather: GEMM1 (128-token tiles) gathers its token rows by TMA; default off
     int fuse_combine;          // b200moe_set_fused_combine: GEMM2 epilogue adds a token's rows up (narrow tiles); default off
     int* d_sync;               // device, 64 bytes, zero between calls: the meeting words of the fused front end
@@ -122,11 +123,19 @@ int num_slices(const b200moe_config& c, int T) {
     return n <= 0 ? 1 : (int)((n + SLICE_PAIRS - 1) / SLICE_PAIRS);
 }
 
-int pick_token_tile(const b200moe_config& c, int T) {
+// Measured on the DeepSeek-V3 shape with 32 local experts (microseconds per forward, tile 16 / 32 / 64 / 128):
+// T=64 149/160/202/187, T=192 211/230/244/225, T=256 230/214/244/227, T=320 247/244/245/219, T=512 308/284/292/279,
+// T=1024 482/372/353/301, T=1792 -/-/463/372.  The 16-token tile wins while an expert sees fewer rows than the tile
+// holds; from about nine expected rows per expert the 128-token tile (tokens on M, one N = 256 MMA per K step) is
+// ahead of every narrower one although most of its rows are padding - the step is bound by the weight stream, and
+// the narrow tiles' weights-on-M MMAs are short of shared-memory bandwidth from 64 columns on.  The 64-token tile is
+// never the best choice; it stays available through b200moe_set_token_tile.
+int pick_token_tile(const b200moe_ctx* h, int T) {
+    if (h->token_tile) return h->token_tile;
+    const b200moe_config& c = h->cfg;
     const double avg = (double)T * c.top_k / c.num_experts;
-    if (avg <= 10.0) return 16;
-    if (avg <= 24.0) return 32;
-    if (avg <= 56.0) return 64;
+    if (avg <= 7.0) return 16;
+    if (avg <= 9.0) return 32;
     return 128;
 }
 
@@ -167,7 +176,7 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     L->sk_count = take((size_t)2 * (4 * h->num_sms + 4) * 4); // [GEMM1 | GEMM2][4 * grid + 4]; zeroed with the head
     L->slices = take((size_t)num_slices(c, T) * El * 4);      // zeroed with the head
     // narrow token tiles: the combine is fused into GEMM2 and counts row deliveries per (token, 256 output columns)
-    L->tok_count = take(pick_token_tile(c, T) < 128 ? (size_t)T * ((c.hidden + 255) / 256) * 4 : 0);   // zeroed with the head
+    L->tok_count = take(pick_token_tile(h, T) < 128 ? (size_t)T * ((c.hidden + 255) / 256) * 4 : 0);   // zeroed with the head
     L->expert_row0 = take((size_t)(El + 1) * 4);
     L->tile_prefix = take((size_t)(El + 1) * 4);
     L->topk_idx = take((size_t)T * K * 4);
@@ -181,10 +190,10 @@ void layout(const b200moe_ctx* h, int T, b200moe_ws_layout* L) {
     L->act_lo = take(rows * c.intermediate);
     L->act_scale = take((size_t)(c.intermediate / 128) * rows * 4);
     L->y = take(rows * c.hidden * 2);
-    L->sk_partial = take(sk_partial_bytes(c, h->num_sms, (int)pick_token_tile(c, T)));
+    L->sk_partial = take(sk_partial_bytes(c, h->num_sms, (int)pick_token_tile(h, T)));
     L->trace = take((size_t)2 * h->num_sms * TRACE_SLOTS * 8 + 2 * 8 * KLOG_N * 8);   // [GEMM1 | GEMM2][CTA][slot], then K-block logs
     L->rows_cap = rows;
-    L->token_tile = (size_t)pick_token_tile(c, T);
+    L->token_tile = (size_t)pick_token_tile(h, T);
     L->total_bytes = off;
 }
 
@@ -574,6 +583,7 @@ int b200moe_create(const b200moe_config* cfg, b200moe_handle* out) {
     h->prof_slots = 0; h->prof_calls = 0; h->prof_events = nullptr;
     h->wait_limit_ns = WAIT_LIMIT_NS;
     { const char* e = getenv("B200MOE_FUSE_COMBINE"); h->fuse_combine = e ? atoi(e) != 0 : 0; }
+    h->token_tile = 0;
     { const char* e = getenv("B200MOE_GATHER4"); h->tma_gather = e ? atoi(e) != 0 : 0; }
     h->d_sync = nullptr;
     if (cudaMalloc(&h->d_sync, 64) != cudaSuccess || cudaMemset(h->d_sync, 0, 64) != cudaSuccess) {
@@ -603,6 +613,12 @@ int b200moe_destroy(b200moe_handle h) {
     b200moe_profile_enable(h, 0);
     cudaFree(h->d_sync);
     delete h;
+    return 0;
+}
+
+int b200moe_set_token_tile(b200moe_handle h, int tokens) {
+    if (!h || (tokens != 0 && tokens != 16 && tokens != 32 && tokens != 64 && tokens != 128)) return B200MOE_E_BADARG;
+    h->token_tile = tokens;
     return 0;
 }
 
@@ -666,8 +682,8 @@ int b200moe_workspace_bytes(b200moe_handle h, int num_tokens, size_t* bytes) {
 int b200moe_launches_per_forward(b200moe_handle h, int num_tokens, int* launches) {
     if (!h || !launches || num_tokens < 0) return B200MOE_E_BADARG;
     // [route, permute, gather | fused route+permute+gather for small T], gemm1, gemm2, [combine unless fused into gemm2]
-    const bool fuse = h->fuse_combine && pick_token_tile(h->cfg, num_tokens) < 128 && !use_pairs(h, pick_token_tile(h->cfg, num_tokens));
-    const bool g4 = pick_token_tile(h->cfg, num_tokens) == 128 && !use_pairs(h, 128) && h->tma_gather;
+    const bool fuse = h->fuse_combine && pick_token_tile(h, num_tokens) < 128 && !use_pairs(h, pick_token_tile(h, num_tokens));
+    const bool g4 = pick_token_tile(h, num_tokens) == 128 && !use_pairs(h, 128) && h->tma_gather;
     *launches = num_tokens == 0 ? 0 : (num_tokens <= FRONT_MAX_T ? 4 : 6) - (fuse ? 1 : 0) - (g4 ? 1 : 0);
     return 0;
 }
@@ -675,7 +691,7 @@ int b200moe_launches_per_forward(b200moe_handle h, int num_tokens, int* launches
 int b200moe_launches_routed(b200moe_handle h, int num_tokens, int* launches) {
     if (!h || !launches || num_tokens < 0) return B200MOE_E_BADARG;
     // count, [permute + gather | both in one launch for small T; no gather when GEMM1 gathers by TMA], gemm1, gemm2, combine
-    const bool g4 = pick_token_tile(h->cfg, num_tokens) == 128 && !use_pairs(h, 128) && h->tma_gather;
+    const bool g4 = pick_token_tile(h, num_tokens) == 128 && !use_pairs(h, 128) && h->tma_gather;
     *launches = num_tokens == 0 ? 0 : (num_tokens <= FRONT_MAX_T ? 5 : 6) - (g4 ? 1 : 0);
     return 0;
 }
@@ -958,7 +974,7 @@ int b200moe_permute_noalloc(b200moe_handle h, const int32_t* topk_idx, const flo
     }
     PlanParams pp;
     pp.T = T; pp.top_k = c.top_k; pp.num_local = El; pp.local_offset = local_offset;
-    pp.token_tile = pick_token_tile(c, T);
+    pp.token_tile = pick_token_tile(h, T);
     pp.topk_idx = topk_idx; pp.topk_w = topk_w; pp.pair_stride = c.top_k;
     pp.status = reinterpret_cast<int*>(scratch);
     pp.counts = reinterpret_cast<int*>(scratch + 256);

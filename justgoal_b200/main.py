@@ -107,6 +107,12 @@ class MoELayer:
         _lib.check(_lib.lib.b200moe_launches_routed(self._h, T, C.byref(n)))
         return n.value
 
+    def set_token_tile(self, tokens: int):
+        """Token tile of the GEMMs: 0 = chosen from the token count (default), else 16, 32, 64 or 128 for every call
+        (tuning and tests).  Workspaces are sized per tile, so the cached ones are dropped."""
+        _lib.check(_lib.lib.b200moe_set_token_tile(self._h, int(tokens)), "b200moe_set_token_tile")
+        self._ws.clear()
+
     def set_tma_gather(self, on: bool):
         """128-token tiles only: GEMM1 gathers its token rows by TMA instead of reading a gathered copy (same bits;
         off by default, measured slower)."""

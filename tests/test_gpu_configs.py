@@ -29,14 +29,17 @@ def _cpu(d):
     return {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in d.items()}
 
 
-def _check_against_oracle(T, weights, boost=None, seed=0):
+def _check_against_oracle(T, weights, boost=None, seed=0, tile=0):
     from justgoal_b200 import MoELayer
     shape = I.DEEPSEEK_V3
     d = _inputs(T, weights, seed, boost)
     layer = MoELayer(shape)
+    if tile:
+        layer.set_token_tile(tile)
     out = layer.forward(*util.op_args(d))
     torch.cuda.synchronize()
     assert layer.status(T) == 0
+    assert not tile or int(layer.layout(T).token_tile) == tile
     r = util.run_oracle(shape, _cpu(d))
     idx = layer.view(T, "topk_idx", torch.int32, (T, shape.top_k)).cpu()
     assert bool(O.routing_sets_equal(idx, r.topk_idx).all())
@@ -49,8 +52,19 @@ def test_decode_t64(ds_weights):
     _check_against_oracle(64, ds_weights)
 
 
-def test_mid_t901(ds_weights):
-    _check_against_oracle(901, ds_weights, seed=7)       # 64-token tiles, ragged counts
+@pytest.mark.parametrize("tile", [0, 32, 64])
+def test_mid_t901(ds_weights, tile):
+    """Ragged counts at full size: the tile the layer picks for 901 tokens (128), and the 32- and 64-token kernel
+    families forced through set_token_tile (several token tiles per expert, claimed chunks)."""
+    _check_against_oracle(901, ds_weights, seed=7, tile=tile)
+
+
+def test_token_tile_choice():
+    """16 tokens while an expert expects about seven rows or fewer, 128 from about nine, 32 in between."""
+    from justgoal_b200 import MoELayer
+    layer = MoELayer(I.DEEPSEEK_V3)
+    got = {T: int(layer.layout(T).token_tile) for T in (1, 64, 224, 256, 288, 320, 901, 4096)}
+    assert got == {1: 16, 64: 16, 224: 16, 256: 32, 288: 32, 320: 128, 901: 128, 4096: 128}
 
 
 def test_prefill_t4096_skewed(ds_weights):

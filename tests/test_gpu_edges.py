@@ -58,13 +58,18 @@ def test_single_token():
     _check_output(shape, d, out)
 
 
+@pytest.mark.parametrize("tile", [0, 16, 32, 64])
 @pytest.mark.parametrize("T", [128, 129, 257])
-def test_around_the_fused_front_end_boundary(T):
+def test_around_the_fused_front_end_boundary(T, tile):
     """T = 128 is the last size of the fused permute + gather launch, 129 the first of the sliced
-    permutation (two slices of 1024 pairs), 257 crosses into a third slice."""
+    permutation (two slices of 1024 pairs), 257 crosses into a third slice.  Run with the tile the layer picks
+    (128 tokens here) and with every narrow kernel family forced (several token tiles per expert)."""
+    from justgoal_b200 import MoELayer
     shape = I.TINY_DS
     d = I.make_inputs(shape, T, seed=22 + T)
-    layer, out = _forward(shape, d)
+    layer = MoELayer(shape)
+    layer.set_token_tile(tile)
+    layer, out = _forward(shape, d, layer)
     _check_output(shape, d, out)
     _check_tables(shape, d, layer, T)
 
@@ -130,6 +135,7 @@ def test_fused_combine_equals_the_combine_kernel_bit_for_bit(shape_name, T, tile
     shape = getattr(I, shape_name)
     d = I.make_inputs(shape, T, seed=70 + T)
     layer = MoELayer(shape)
+    layer.set_token_tile(tile)                         # every narrow kernel family, whatever the layer would pick
     assert layer.launches_per_forward(T) == (4 if T <= 128 else 6)
     layer.set_fused_combine(True)                      # off by default
     assert layer.launches_per_forward(T) == (3 if T <= 128 else 5)
