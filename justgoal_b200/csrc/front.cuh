@@ -1,13 +1,18 @@
-// Fused permutation + gather for small token counts (T <= FRONT_MAX_T): histogram, scan, stable
-// permutation and the expert-sorted activation gather in ONE launch after the routing kernel.
+// Front end for small token counts (T <= FRONT_MAX_T): routing, histogram, scan, stable permutation and the
+// expert-sorted activation gather in ONE launch (front_route_kernel; front_small_kernel is the same without the
+// routing, for tokens that were routed elsewhere).
 //
-// With a few dozen tokens the separate kernels are pure launch latency, so every CTA of this
-// kernel redoes the (tiny, integer) histogram and permutation for ALL tokens in its own shared
-// memory - no CTA ever waits for another - and then copies its share of the rows.  CTA 0 alone
-// writes the tables that later kernels read (counts, row maps); all CTAs derive identical values.
-// Same results as count_kernel + permute_kernel + gather_kernel (permute.cuh); the reference
-// fuses the same stages for small batches
-// (kda05_reproduction_full_shape/fable-5.1/moe_fp8_fwd/<def>/fable51_moe_v94/kernel.cu:724-806).
+// With a few dozen tokens separate kernels are pure launch latency.  The tokens are routed one per warp over the CTAs;
+// the CTAs meet once (the routing result of every token must be visible); then every CTA redoes the tiny integer
+// work - histogram, scan, ranks - for ALL tokens in its own shared memory, so no CTA waits for another again, and
+// copies its share of the rows.  One thread owns one (token, expert) pair: its rank inside its expert is its rank
+// among the same-expert pairs of its warp (match.any) plus the counts of the warps before it, which keeps the rows of
+// an expert in token order.  CTA 0 alone writes the tables that later kernels read (counts, row maps); all CTAs
+// derive identical values.  Same results as count_kernel + permute_kernel + gather_kernel (permute.cuh).
+// The next kernel (GEMM1) does not wait for this one to finish before it starts to work: see ST_ROUTED below and
+// GemmParams::routed.  The reference fuses the same stages for small batches
+// (kda05_reproduction_full_shape/fable-5.1/moe_fp8_fwd/<def>/fable51_moe_v94/kernel.cu:724-806) and issues its first
+// weight stages during the table build (its MOE_EARLY_W switch, same directory, main.py:50).
 #pragma once
 #include "permute.cuh"
 #include "routing.cuh"
