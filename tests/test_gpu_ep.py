@@ -36,6 +36,8 @@ def _worker(rank, world, port, out_q, exchange):
                          tokens["hidden_states"].view(torch.uint8)[sl].cuda().view(torch.float8_e4m3fn),
                          tokens["hidden_states_scale"][:, sl].contiguous().cuda(), RSF)
         torch.cuda.synchronize()
+        # route, [pack, unpack | push, barrier, barrier], the local experts (5 or 6 launches), owner-side sum
+        assert ep.launches_per_step() in ((10, 11) if ep.peer is not None else (9, 10))
         if ep.peer is not None:
             # a second step on the same buffers (slots are reused, epochs grow), then the barriers' status
             out = ep.forward(tokens["routing_logits"][sl].cuda(), tokens["routing_bias"].cuda(),
