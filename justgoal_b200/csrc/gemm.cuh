@@ -309,7 +309,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CU
     int* s_row0 = s_tiles + (MAX_LOCAL + 1);
     int* s_cnt = s_row0 + (MAX_LOCAL + 1);
     uint32_t* s_red = reinterpret_cast<uint32_t*>(s_cnt + (MAX_LOCAL + 1));
-    int* s_flag = reinterpret_cast<int*>(s_red + C::NPW * C::NC);   // [NGRP] arrival order of a split unit, per group
+    int* s_flag = reinterpret_cast<int*>(s_red + C::NPW * C::NC);   // 8 ints: [0] routing flag seen (early schedule), [4..5] the producer's chunk sizing
     // [128] token of every row of the producer's unit, 16-byte aligned (read and written as int4)
     int* s_g4 = reinterpret_cast<int*>((reinterpret_cast<uintptr_t>(s_flag + 8) + 15) & ~uintptr_t(15));
 
